@@ -1,0 +1,66 @@
+// Shared device helpers for the sm_100a kernels of this library.
+//
+// Conventions that every kernel file follows:
+//   * activations are packed [tokens, features] row-major; weights are [out, in] row-major;
+//   * T is the working type (float or __nv_bfloat16); sums, norms, softmax and angles are float;
+//   * rnd<T>(x) rounds a float to the working type and back, which places the casts where the
+//     reference's formulas place them (engine/engine.py:75-109) and is the identity for float;
+//   * every extern "C" entry returns 0 or a cudaError_t from the launch, never throws, never
+//     allocates, and runs on the stream it is given.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define SB_PAGE_TOKENS 64
+
+typedef __nv_bfloat16 bf16;
+
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<bf16>(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+template <typename T> __device__ __forceinline__ float rnd(float v) { return to_f<T>(from_f<T>(v)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  `scratch` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int warps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < warps ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  float out = scratch[32];
+  __syncthreads();
+  return out;
+}
+
+// Address of element (page, head, offset, 0) in a paged key or value store laid out
+// [pages][kv_heads][SB_PAGE_TOKENS][head_dim].
+__device__ __forceinline__ size_t page_row(int page, int head, int offset, int kv_heads, int head_dim) {
+  return (((size_t)page * kv_heads + head) * SB_PAGE_TOKENS + offset) * (size_t)head_dim;
+}
+
+#define SB_LAUNCH_RESULT() ((int)cudaGetLastError())

@@ -1,0 +1,131 @@
+// Row-wise kernels: embedding gather, RMSNorm (plain, fused with the residual sum, and on selected
+// rows), and the gated activation.  One block per row; the row is walked twice (sum of squares, then
+// scale) by the same threads over the same columns, so the second pass reads what the first just
+// touched.  Formulas and cast placement: engine/engine.py:75-88 (norm), engine/kernels/fused.py:115-144
+// (sum in float, rounded to the working type, stored, then normed), fused.py:89-112 (silu rounded to
+// the working type before the product).
+#include "common.cuh"
+
+// ------------------------------------------------------------------------------------ embedding
+
+template <typename T>
+__global__ void embedding_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
+                                 T* __restrict__ out, int hidden, int vocab, int* status) {
+  const int row = blockIdx.x;
+  int tok = tokens[row];
+  const bool bad = tok < 0 || tok >= vocab;
+  if (bad) {
+    if (threadIdx.x == 0 && status) atomicOr(status, 1);
+    tok = 0;
+  }
+  const T* src = table + (size_t)tok * hidden;
+  T* dst = out + (size_t)row * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = bad ? from_f<T>(0.f) : src[c];
+}
+
+// ------------------------------------------------------------------------------------ norms
+
+// y[r] = gain * round(x[r] * rsqrt(mean(x[r]^2) + eps)).  With `delta`, x[r] is first replaced by
+// round(x[r] + delta[r]) and written back (the residual stream).  With `rows`, output row i comes
+// from input row rows[i] and nothing is written back.
+template <typename T, typename W, bool ADD, bool WRITE_BACK>
+__global__ void rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delta,
+                               const W* __restrict__ gain, T* __restrict__ y,
+                               const int* __restrict__ rows, int hidden, float eps) {
+  __shared__ float scratch[33];
+  const int out_row = blockIdx.x;
+  const int in_row = rows ? rows[out_row] : out_row;
+  T* xr = x + (size_t)in_row * hidden;
+  const T* dr = ADD ? delta + (size_t)in_row * hidden : nullptr;
+  T* yr = y + (size_t)out_row * hidden;
+
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float v = to_f<T>(xr[c]);
+    if (ADD) {
+      v = rnd<T>(v + to_f<T>(dr[c]));
+      if (WRITE_BACK) xr[c] = from_f<T>(v);
+    }
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)hidden + eps);
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float v = to_f<T>(xr[c]);
+    if (ADD && !WRITE_BACK) v = rnd<T>(v + to_f<T>(dr[c]));
+    yr[c] = from_f<T>(rnd<T>(v * inv) * to_f<W>(gain[c]));
+  }
+}
+
+template <typename T, typename W>
+static int launch_rmsnorm(void* x, const void* delta, const void* gain, void* y, const int* rows,
+                          int n_rows, int hidden, float eps, cudaStream_t s) {
+  if (n_rows == 0) return 0;
+  int threads = hidden >= 4096 ? 1024 : hidden >= 1024 ? 512 : hidden >= 256 ? 256 : 128;
+  T* xp = (T*)x;
+  const T* dp = (const T*)delta;
+  const W* gp = (const W*)gain;
+  T* yp = (T*)y;
+  if (delta && !rows)
+    rmsnorm_kernel<T, W, true, true><<<n_rows, threads, 0, s>>>(xp, dp, gp, yp, rows, hidden, eps);
+  else if (delta)
+    rmsnorm_kernel<T, W, true, false><<<n_rows, threads, 0, s>>>(xp, dp, gp, yp, rows, hidden, eps);
+  else
+    rmsnorm_kernel<T, W, false, false><<<n_rows, threads, 0, s>>>(xp, dp, gp, yp, rows, hidden, eps);
+  return SB_LAUNCH_RESULT();
+}
+
+// ------------------------------------------------------------------------------------ gated activation
+
+// act[r, c] = round(silu(gate)) * up with gate = gu[r, c], up = gu[r, inner + c].
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, int inner, size_t total) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    const size_t row = i / inner;
+    const int col = (int)(i - row * inner);
+    const float g = to_f<T>(gu[row * 2 * inner + col]);
+    const float u = to_f<T>(gu[row * 2 * inner + inner + col]);
+    const float silu = rnd<T>(g / (1.f + expf(-g)));
+    act[i] = from_f<T>(silu * u);
+  }
+}
+
+extern "C" {
+
+// dtype: 0 float, 1 bfloat16.  gain_dtype likewise.
+int sb_embedding(int dtype, const int* tokens, const void* table, void* out, int n_tokens, int hidden,
+                 int vocab, int* status, cudaStream_t s) {
+  if (n_tokens == 0) return 0;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (dtype == 0)
+    embedding_kernel<float><<<n_tokens, threads, 0, s>>>(tokens, (const float*)table, (float*)out, hidden, vocab, status);
+  else
+    embedding_kernel<bf16><<<n_tokens, threads, 0, s>>>(tokens, (const bf16*)table, (bf16*)out, hidden, vocab, status);
+  return SB_LAUNCH_RESULT();
+}
+
+// x: [*, hidden] read (and, with delta and without rows, updated in place); y: [n_rows, hidden].
+int sb_rmsnorm(int dtype, int gain_dtype, void* x, const void* delta, const void* gain, void* y,
+               const int* rows, int n_rows, int hidden, float eps, cudaStream_t s) {
+  if (dtype == 0 && gain_dtype == 0) return launch_rmsnorm<float, float>(x, delta, gain, y, rows, n_rows, hidden, eps, s);
+  if (dtype == 1 && gain_dtype == 1) return launch_rmsnorm<bf16, bf16>(x, delta, gain, y, rows, n_rows, hidden, eps, s);
+  if (dtype == 1 && gain_dtype == 0) return launch_rmsnorm<bf16, float>(x, delta, gain, y, rows, n_rows, hidden, eps, s);
+  return -1;
+}
+
+int sb_swiglu(int dtype, const void* gu, void* act, int n_rows, int inner, cudaStream_t s) {
+  const size_t total = (size_t)n_rows * inner;
+  if (total == 0) return 0;
+  const int threads = 256;
+  size_t blocks = (total + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == 0)
+    swiglu_kernel<float><<<(int)blocks, threads, 0, s>>>((const float*)gu, (float*)act, inner, total);
+  else
+    swiglu_kernel<bf16><<<(int)blocks, threads, 0, s>>>((const bf16*)gu, (bf16*)act, inner, total);
+  return SB_LAUNCH_RESULT();
+}
+
+}  // extern "C"

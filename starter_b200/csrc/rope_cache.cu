@@ -1,0 +1,131 @@
+// Per-head q/k RMSNorm, rotary positions and the write of keys and values into the paged cache, in
+// one pass over the fused projection output.  One warp per (token, head) row of head_dim values.
+//
+// Formulas (engine/engine.py:699-718, engine/kernels/fused.py:161-219 and 553-617): the head row is
+// normed with the gain shared by all heads (normalised value rounded to the working type, then times
+// the gain), then rotated half-split: out[j] = n[j]*cos[j] - n[j+half]*sin[j], out[j+half] =
+// n[j+half]*cos[j] + n[j]*sin[j], each product and the sum rounded to the working type, cos and sin
+// rounded to the working type first.  Values are copied unchanged.  The cache position of a token is
+// its absolute position in its sequence: page block_table[slot][pos / 64], offset pos % 64.
+#include "common.cuh"
+
+#define SB_MAX_PAIRS 4  // head_dim <= 256
+
+template <typename T, typename W>
+__global__ void qk_norm_rope_store_kernel(
+    const T* __restrict__ qkv, T* __restrict__ q_out, const W* __restrict__ q_gain,
+    const W* __restrict__ k_gain, const float* __restrict__ cos_table,
+    const float* __restrict__ sin_table, const int* __restrict__ tok_pos,
+    const int* __restrict__ tok_slot, const int* __restrict__ block_table, int table_stride,
+    T* __restrict__ k_store, T* __restrict__ v_store, int n_tokens, int heads, int kv_heads,
+    int head_dim, float eps, int heads_per_token, int row_stride) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= n_tokens * heads_per_token) return;
+  const int token = warp / heads_per_token;
+  const int h = warp - token * heads_per_token;
+  const int half = head_dim >> 1;
+  const T* src = qkv + (size_t)token * row_stride + (size_t)h * head_dim;
+  const int pos = tok_pos[token];
+
+  T* dst;
+  const bool is_q = h < heads;
+  const bool is_v = h >= heads + kv_heads;
+  if (is_q) {
+    dst = q_out + ((size_t)token * heads + h) * head_dim;
+  } else {
+    const int kvh = is_v ? h - heads - kv_heads : h - heads;
+    const int page = block_table[(size_t)tok_slot[token] * table_stride + pos / SB_PAGE_TOKENS];
+    T* store = is_v ? v_store : k_store;
+    dst = store + page_row(page, kvh, pos % SB_PAGE_TOKENS, kv_heads, head_dim);
+  }
+
+  if (is_v) {
+    for (int d = lane; d < head_dim; d += 32) dst[d] = src[d];
+    return;
+  }
+
+  float lo[SB_MAX_PAIRS], hi[SB_MAX_PAIRS];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < SB_MAX_PAIRS; ++i) {
+    const int j = lane + 32 * i;
+    lo[i] = hi[i] = 0.f;
+    if (j < half) {
+      lo[i] = to_f<T>(src[j]);
+      hi[i] = to_f<T>(src[j + half]);
+      ss += lo[i] * lo[i] + hi[i] * hi[i];
+    }
+  }
+  const W* gain = is_q ? q_gain : k_gain;
+  if (gain) {
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)head_dim + eps);
+#pragma unroll
+    for (int i = 0; i < SB_MAX_PAIRS; ++i) {
+      const int j = lane + 32 * i;
+      if (j < half) {
+        lo[i] = rnd<T>(rnd<T>(lo[i] * inv) * to_f<W>(gain[j]));
+        hi[i] = rnd<T>(rnd<T>(hi[i] * inv) * to_f<W>(gain[j + half]));
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < SB_MAX_PAIRS; ++i) {
+    const int j = lane + 32 * i;
+    if (j < half) {
+      float out_lo = lo[i], out_hi = hi[i];
+      if (cos_table) {
+        const float c = rnd<T>(cos_table[(size_t)pos * half + j]);
+        const float s = rnd<T>(sin_table[(size_t)pos * half + j]);
+        out_lo = rnd<T>(rnd<T>(lo[i] * c) + rnd<T>(-hi[i] * s));
+        out_hi = rnd<T>(rnd<T>(hi[i] * c) + rnd<T>(lo[i] * s));
+      }
+      dst[j] = from_f<T>(out_lo);
+      dst[j + half] = from_f<T>(out_hi);
+    }
+  }
+}
+
+template <typename T, typename W>
+static int launch(const void* qkv, void* q_out, const void* q_gain, const void* k_gain,
+                  const float* cos_table, const float* sin_table, const int* tok_pos,
+                  const int* tok_slot, const int* block_table, int table_stride, void* k_store,
+                  void* v_store, int n_tokens, int heads, int kv_heads, int head_dim, float eps,
+                  int write_cache, int row_stride, cudaStream_t s) {
+  const int per_token = write_cache ? heads + 2 * kv_heads : heads;
+  const long long warps = (long long)n_tokens * per_token;
+  if (warps == 0) return 0;
+  const int threads = 128;
+  const long long blocks = (warps * 32 + threads - 1) / threads;
+  qk_norm_rope_store_kernel<T, W><<<(unsigned)blocks, threads, 0, s>>>(
+      (const T*)qkv, (T*)q_out, (const W*)q_gain, (const W*)k_gain, cos_table, sin_table, tok_pos,
+      tok_slot, block_table, table_stride, (T*)k_store, (T*)v_store, n_tokens, heads, kv_heads,
+      head_dim, eps, per_token, row_stride);
+  return SB_LAUNCH_RESULT();
+}
+
+extern "C" {
+
+// qkv: [n_tokens, (heads + 2*kv_heads) * head_dim]; q_out: [n_tokens, heads * head_dim].
+// q_gain / k_gain may be null (no per-head norm); cos_table / sin_table [positions, head_dim/2]
+// float may be null (no rotation).  Rows of qkv are row_stride elements apart.  With
+// write_cache == 0 only the query heads are processed, so qkv may hold the queries alone.
+int sb_qk_norm_rope_store(int dtype, int gain_dtype, const void* qkv, void* q_out, const void* q_gain,
+                          const void* k_gain, const float* cos_table, const float* sin_table,
+                          const int* tok_pos, const int* tok_slot, const int* block_table,
+                          int table_stride, void* k_store, void* v_store, int n_tokens, int heads,
+                          int kv_heads, int head_dim, float eps, int write_cache, int row_stride,
+                          cudaStream_t s) {
+  if (head_dim > 64 * SB_MAX_PAIRS || (head_dim & 1)) return -2;
+#define ARGS qkv, q_out, q_gain, k_gain, cos_table, sin_table, tok_pos, tok_slot, block_table, \
+             table_stride, k_store, v_store, n_tokens, heads, kv_heads, head_dim, eps, write_cache, \
+             row_stride, s
+  if (dtype == 0 && gain_dtype == 0) return launch<float, float>(ARGS);
+  if (dtype == 1 && gain_dtype == 1) return launch<bf16, bf16>(ARGS);
+  if (dtype == 1 && gain_dtype == 0) return launch<bf16, float>(ARGS);
+#undef ARGS
+  return -1;
+}
+
+}  // extern "C"

@@ -1,0 +1,151 @@
+"""The generic decoder: an embedding, layers built from parts, a run order, a final norm and a head.
+
+Everything model-specific arrives in the ``ModelSpec``.  ``expected_tensors``
+derives from the spec the checkpoint names and shapes the model wants; ``forward``
+runs one step over a packed batch (see ``starter_b200.engine.batch``) and returns
+float32 logits for the wanted rows only, as the reference computes the head for
+the last position only (engine/engine.py:801-803).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..parts import ParamSpec, lookup
+
+
+def build_layers(spec, dtype, device):
+    """Instantiate every layer's parts; position parts with equal specs are shared."""
+    positions = {}
+    blocks = []
+    for layer in spec.layers:
+        pos_spec = getattr(layer.mixer, "position", None)
+        position = None
+        if pos_spec is not None:
+            if pos_spec not in positions:
+                positions[pos_spec] = lookup("position", pos_spec.kind)(pos_spec, dtype, device)
+            position = positions[pos_spec]
+        mixer = lookup("mixer", layer.mixer.kind)(layer.mixer, dtype, position)
+        feed_forward = lookup("feed_forward", layer.feed_forward.kind)(layer.feed_forward, dtype)
+        norm1 = lookup("norm", layer.norm1.kind)(layer.norm1, dtype)
+        norm2 = lookup("norm", layer.norm2.kind)(layer.norm2, dtype)
+        blocks.append(lookup("arrangement", layer.arrangement)(mixer, feed_forward, norm1, norm2))
+    return blocks, list(positions.values())
+
+
+def _layer_params(block, names: dict) -> dict:
+    """``{checkpoint name: (part name, logical name, ParamSpec)}`` for one block."""
+    out = {}
+    for part_name, part in block.parts().items():
+        for logical, pspec in part.param_specs().items():
+            key = f"{part_name}.{logical}"
+            if key not in names:
+                raise ValueError(f"the layer spec names no checkpoint tensor for {key}")
+            out[names[key]] = (part_name, logical, pspec)
+    return out
+
+
+def expected_tensors(spec) -> dict:
+    """``{checkpoint name: ParamSpec}`` in a fixed order: embedding, layers, final norm, head."""
+    blocks, _ = build_layers(spec, torch.float32, "cpu")
+    out = {spec.embed_name: ParamSpec((spec.vocab_size, spec.hidden_size))}
+    for block, layer in zip(blocks, spec.layers):
+        for name, (_, _, pspec) in _layer_params(block, layer.names).items():
+            out[name] = pspec
+    out[spec.final_norm_name] = ParamSpec((spec.final_norm.size,), "gain")
+    if not spec.tie_embeddings:
+        out[spec.lm_head_name] = ParamSpec((spec.vocab_size, spec.hidden_size))
+    return out
+
+
+class DecoderModel:
+    def __init__(self, spec, dtype, device="cuda"):
+        self.spec = spec
+        self.dtype = dtype
+        self.device = torch.device(device)
+        self.blocks, self.positions = build_layers(spec, dtype, self.device)
+        self.final_norm = lookup("norm", spec.final_norm.kind)(spec.final_norm, dtype)
+        self.embed = None
+        self.lm_head = None
+        for entry in spec.schedule:
+            if not 0 <= entry.layer < len(self.blocks):
+                raise ValueError(f"the run order names layer {entry.layer}; the model has {len(self.blocks)}")
+        writers = {}
+        for entry in spec.schedule:
+            if entry.writes_cache:
+                writers.setdefault(entry.cache, entry.layer)
+        for entry in spec.schedule:
+            if not entry.writes_cache and entry.cache not in writers:
+                raise ValueError(f"cache entry {entry.cache} is read but no entry of the run order writes it")
+
+    # ------------------------------------------------------------------ weights
+
+    def expected_tensors(self) -> dict:
+        return expected_tensors(self.spec)
+
+    def load_tensors(self, tensors: dict) -> None:
+        """Take ``{checkpoint name: device tensor}`` (already placed by the loader)."""
+        spec = self.spec
+        self.embed = tensors[spec.embed_name]
+        self.lm_head = self.embed if spec.tie_embeddings else tensors[spec.lm_head_name]
+        self.final_norm.set_params({"weight": tensors[spec.final_norm_name]})
+        for block, layer in zip(self.blocks, spec.layers):
+            grouped = {}
+            for name, (part_name, logical, _) in _layer_params(block, layer.names).items():
+                grouped.setdefault(part_name, {})[logical] = tensors[name]
+            for part_name, part in block.parts().items():
+                if part.param_specs():
+                    part.set_params(grouped[part_name])
+
+    # ------------------------------------------------------------------ cache needs
+
+    def kv_needs(self) -> dict:
+        """``{cache entry: KVNeed}``, taken from the entry's writer."""
+        needs = {}
+        for entry in self.spec.schedule:
+            if entry.writes_cache and entry.cache not in needs:
+                needs[entry.cache] = self.blocks[entry.layer].mixer.kv_need()
+        return needs
+
+    def state_needs(self) -> dict:
+        needs = {}
+        for entry in self.spec.schedule:
+            if entry.writes_cache and entry.cache not in needs:
+                needs[entry.cache] = self.blocks[entry.layer].mixer.state_need()
+        return needs
+
+    # ------------------------------------------------------------------ compute
+
+    def prepare(self, max_position: int) -> None:
+        """Host-side growth (position tables) that must not happen in the middle of a step."""
+        for block in self.blocks:
+            block.mixer.prepare(max_position)
+
+    def hidden(self, ctx):
+        """Run the layers; returns ``(residual, pending)`` with the last sum still open."""
+        residual = ops.embedding(ctx.tokens, self.embed, ctx.status)
+        pending = None
+        for entry in self.spec.schedule:
+            residual, pending = self.blocks[entry.layer](residual, pending, ctx, entry.cache,
+                                                         entry.writes_cache)
+        return residual, pending
+
+    def logits(self, residual, pending, rows):
+        """Float32 logits ``[len(rows), vocab]`` of the rows asked for."""
+        h = self.final_norm.add_rows(residual, pending, rows)
+        return ops.linear(h, self.lm_head, out_float=True)
+
+    def forward(self, ctx, rows):
+        residual, pending = self.hidden(ctx)
+        if rows is None or rows.numel() == 0:
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+        return self.logits(residual, pending, rows)
+
+    def step_weight_bytes(self) -> int:
+        """Bytes of weights one decode step reads: every layer the run order names, each time it is
+        named, the final norm and the head (the embedding table is only gathered from)."""
+        total = self.final_norm.weight_bytes() + self.lm_head.numel() * self.lm_head.element_size()
+        for entry in self.spec.schedule:
+            total += sum(p.weight_bytes() for p in self.blocks[entry.layer].parts().values())
+        return total

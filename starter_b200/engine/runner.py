@@ -1,0 +1,130 @@
+"""The step function: runs exactly the tokens it is given, as one batch, from the cache.
+
+``ModelRunner`` owns a loaded model and its cache.  ``step`` takes, for each
+sequence of the batch, its slot, its next tokens and the places whose logits are
+wanted, writes those tokens' keys and values behind what the sequence already
+holds, and returns float32 logits ``[wanted, vocab]`` in the order of the entries
+and of their ``want`` lists.  A whole prompt, a later chunk of one and a single
+token are the same call; sequences of a step may bring different numbers of
+tokens.  (The reference has two functions for this, ``_forward_prefill`` and
+``_forward_decode``, engine/engine.py:738-839, and needs equal lengths.)
+"""
+
+from __future__ import annotations
+
+import os
+
+import torch
+
+from ..cache import SequenceCache
+from ..config import load_config
+from ..weights import load_checkpoint
+from .batch import StepContext, StepEntry, plan_step, upload
+from .model import DecoderModel
+
+DTYPES = {
+    "bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
+    "float32": torch.float32, "fp32": torch.float32,
+}
+
+
+def resolve_dtype(dtype):
+    if isinstance(dtype, torch.dtype):
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"dtype must be float32 or bfloat16, not {dtype}")
+        return dtype
+    try:
+        return DTYPES[str(dtype)]
+    except KeyError:
+        raise ValueError(f"dtype must be one of {sorted(DTYPES)}, not {dtype!r}") from None
+
+
+def require_cuda(device="cuda:0") -> torch.device:
+    if not torch.cuda.is_available():
+        raise RuntimeError("starter_b200 runs on a CUDA device (sm_100a); none is visible and there is "
+                           "no CPU implementation")
+    device = torch.device(device)
+    if device.type != "cuda":
+        raise RuntimeError(f"starter_b200 runs on CUDA devices only, not {device}")
+    torch.cuda.set_device(device)
+    # no reduced-precision matrix modes anywhere (engine/engine.py:119-122)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+    return device
+
+
+def load_model(model_dir: str, dtype="bfloat16", device="cuda:0") -> DecoderModel:
+    """Build the model ``model_dir/config.json`` names and load its safetensors weights."""
+    device = require_cuda(device)
+    dtype = resolve_dtype(dtype)
+    config = load_config(model_dir)
+    spec = config.to_model_spec()
+    model = DecoderModel(spec, dtype, device)
+    alias = (spec.lm_head_name, spec.embed_name) if spec.tie_embeddings else None
+    tensors = load_checkpoint(model_dir, model.expected_tensors(), dtype, device, tied_alias=alias)
+    model.load_tensors(tensors)
+    model.config = config
+    return model
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, max_tokens: int, max_sequences: int | None = None,
+                 max_sequence_tokens: int | None = None):
+        self.model = model
+        self.device = model.device
+        pages = (max_tokens + 63) // 64
+        if max_sequences is None:
+            max_sequences = min(pages, 1024)
+        self.cache = SequenceCache(model.kv_needs(), model.state_needs(), max_tokens, max_sequences,
+                                   model.dtype, self.device, max_sequence_tokens)
+        self.status = torch.zeros((1,), dtype=torch.int32, device=self.device)
+
+    # ------------------------------------------------------------------ sequences
+
+    def open_sequence(self) -> int:
+        return self.cache.open_sequence()
+
+    def close_sequence(self, slot: int) -> None:
+        self.cache.close_sequence(slot)
+
+    # ------------------------------------------------------------------ the step
+
+    def make_context(self, entries) -> StepContext:
+        cache = self.cache
+        for e in entries:
+            cache.reserve(e.slot, cache.lengths[e.slot] + len(e.tokens))
+        starts = [cache.lengths[e.slot] for e in entries]
+        arrays = plan_step(entries, starts, self.model.spec.vocab_size)
+        for e in entries:
+            cache.advance(e.slot, len(e.tokens))
+        cache.sync_table()
+        dev = upload(arrays, self.device)
+        max_kv = int(arrays["seq_kv_len"].max())
+        self.model.prepare(max_kv)
+        return StepContext(
+            n_tokens=int(arrays["tokens"].size), n_seqs=len(entries),
+            tokens=dev["tokens"], tok_pos=dev["tok_pos"], tok_slot=dev["tok_slot"],
+            seq_slot=dev["seq_slot"], seq_q_start=dev["seq_q_start"], seq_q_len=dev["seq_q_len"],
+            seq_kv_len=dev["seq_kv_len"], want_rows=dev["want_rows"],
+            max_q_len=int(arrays["seq_q_len"].max()), max_kv_len=max_kv,
+            cache=cache, status=self.status, host=arrays)
+
+    @torch.inference_mode()
+    def step(self, entries) -> torch.Tensor:
+        """Run one step; ``entries`` is a list of ``StepEntry``.  Returns ``[wanted, vocab]`` float32."""
+        entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        ctx = self.make_context(entries)
+        return self.model.forward(ctx, ctx.want_rows)
+
+    def check_status(self) -> None:
+        """Raise if a kernel flagged a bad input since the last check (reads one int from the device)."""
+        code = int(self.status.item())
+        if code:
+            self.status.zero_()
+            problems = []
+            if code & 1:
+                problems.append("a token id outside the vocabulary reached the embedding")
+            if code & 2:
+                problems.append("a row of logits held no finite value")
+            raise RuntimeError("; ".join(problems) or f"device status {code}")

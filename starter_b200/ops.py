@@ -1,0 +1,262 @@
+"""Python face of the CUDA kernels: argument checks, output allocation, launch on the current stream.
+
+Every function here runs a hand-written kernel from ``starter_b200/csrc`` (the one
+exception, the prompt-sized bfloat16 matrix product, goes to the vendor's GEMM
+library exactly where the reference does, engine/engine.py:431-450).  There is no
+CPU path: tensors must live on a CUDA device, and a shape a kernel cannot take is
+refused with an error that names it.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .csrc import build
+
+PAGE_TOKENS = 64
+SMALL_ROWS = 16
+MAX_HEAD_DIM = 256
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _code(dtype) -> int:
+    if dtype not in _DT:
+        raise KernelError(f"kernels take float32 or bfloat16 tensors, not {dtype}")
+    return _DT[dtype]
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need(t, name, dtype=None, ndim=None):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (there is no CPU implementation)")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous, got strides {t.stride()} for shape {tuple(t.shape)}")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if ndim is not None and t.dim() != ndim:
+        raise KernelError(f"{name} must have {ndim} dimensions, got shape {tuple(t.shape)}")
+
+
+def _check(rc, what):
+    if rc != 0:
+        if rc == -1:
+            raise KernelError(f"{what}: this combination of dtypes has no kernel")
+        if rc == -2:
+            raise KernelError(f"{what}: a size is outside what the kernel takes")
+        raise KernelError(f"{what}: launch failed with CUDA error {rc}")
+
+
+def _gain_code(x, gain):
+    if gain.dtype == torch.float32:
+        return 0
+    if gain.dtype == torch.bfloat16 and x.dtype == torch.bfloat16:
+        return 1
+    raise KernelError(f"a {gain.dtype} gain cannot scale {x.dtype} activations")
+
+
+# ---------------------------------------------------------------------------------------- rows
+
+def embedding(tokens, table, status=None):
+    """``out[t] = table[tokens[t]]``; ``tokens`` int32 ``[T]``, ``table`` ``[V, H]``."""
+    _need(tokens, "tokens", torch.int32, 1)
+    _need(table, "table", None, 2)
+    out = torch.empty((tokens.shape[0], table.shape[1]), dtype=table.dtype, device=table.device)
+    rc = build.load("elementwise").sb_embedding(
+        _code(table.dtype), _ptr(tokens), _ptr(table), _ptr(out), tokens.shape[0], table.shape[1],
+        table.shape[0], _ptr(status), _stream())
+    _check(rc, "embedding")
+    return out
+
+
+def rmsnorm(x, gain, eps, delta=None, rows=None, out=None):
+    """RMSNorm of the rows of ``x`` ``[T, H]``.
+
+    With ``delta`` the norm is taken of ``x + delta`` and, unless ``rows`` is given,
+    ``x`` is replaced by that sum (the residual stream).  With ``rows`` (int32
+    ``[R]``) only those rows are normed and ``x`` is left alone.
+    """
+    _need(x, "x", None, 2)
+    _need(gain, "gain", None, 1)
+    hidden = x.shape[1]
+    if gain.shape[0] != hidden:
+        raise KernelError(f"gain has {gain.shape[0]} entries for rows of {hidden}")
+    if delta is not None:
+        _need(delta, "delta", x.dtype, 2)
+        if delta.shape != x.shape:
+            raise KernelError(f"delta {tuple(delta.shape)} does not match x {tuple(x.shape)}")
+    n_rows = x.shape[0]
+    if rows is not None:
+        _need(rows, "rows", torch.int32, 1)
+        n_rows = rows.shape[0]
+    if out is None:
+        out = torch.empty((n_rows, hidden), dtype=x.dtype, device=x.device)
+    rc = build.load("elementwise").sb_rmsnorm(
+        _code(x.dtype), _gain_code(x, gain), _ptr(x), _ptr(delta), _ptr(gain), _ptr(out), _ptr(rows),
+        n_rows, hidden, ctypes.c_float(eps), _stream())
+    _check(rc, "rmsnorm")
+    return out
+
+
+def swiglu(gate_up):
+    """``round(silu(gate)) * up`` for ``gate_up = [gate | up]`` of shape ``[T, 2 * I]``."""
+    _need(gate_up, "gate_up", None, 2)
+    if gate_up.shape[1] % 2:
+        raise KernelError(f"gate_up has an odd width {gate_up.shape[1]}")
+    inner = gate_up.shape[1] // 2
+    out = torch.empty((gate_up.shape[0], inner), dtype=gate_up.dtype, device=gate_up.device)
+    rc = build.load("elementwise").sb_swiglu(
+        _code(gate_up.dtype), _ptr(gate_up), _ptr(out), gate_up.shape[0], inner, _stream())
+    _check(rc, "swiglu")
+    return out
+
+
+# ---------------------------------------------------------------------------------------- matrix products
+
+def linear(x, weight, out_float=False, gated=False):
+    """``x @ weight.T`` for ``x`` ``[T, K]`` and ``weight`` ``[N, K]`` (no bias).
+
+    ``gated``: ``weight`` is ``[gate; up]`` stacked (``[2 * I, K]``) and the result is
+    ``round(silu(x @ gate.T)) * (x @ up.T)`` of shape ``[T, I]``.  ``out_float``
+    returns float32 whatever the working type (used for logits).
+    """
+    _need(x, "x", None, 2)
+    _need(weight, "weight", x.dtype, 2)
+    rows, k_dim = x.shape
+    if weight.shape[1] != k_dim:
+        raise KernelError(f"weight {tuple(weight.shape)} does not take inputs of width {k_dim}")
+    n_total = weight.shape[0]
+    if gated and n_total % 2:
+        raise KernelError(f"a gated weight needs an even number of rows, got {n_total}")
+    n_out = n_total // 2 if gated else n_total
+    dt = _code(x.dtype)
+    if rows <= SMALL_ROWS:
+        out_dtype = torch.float32 if (out_float or dt == 0) else x.dtype
+        if gated and out_float and dt == 1:
+            raise KernelError("a gated product cannot return float32 from bfloat16")
+        y = torch.empty((rows, n_out), dtype=out_dtype, device=x.device)
+        rc = build.load("linear_small").sb_linear_small(
+            dt, int(out_float), int(gated), _ptr(x), _ptr(weight), _ptr(y), rows, n_out, k_dim,
+            _stream())
+        _check(rc, "linear_small")
+        return y
+    if dt == 0:
+        y = torch.empty((rows, n_total), dtype=torch.float32, device=x.device)
+        rc = build.load("sgemm").sb_sgemm_nt(_ptr(x), _ptr(weight), _ptr(y), rows, n_total, k_dim,
+                                             _stream())
+        _check(rc, "sgemm")
+    elif out_float:
+        y = torch.mm(x, weight.t(), out_dtype=torch.float32)
+    else:
+        y = torch.mm(x, weight.t())
+    return swiglu(y) if gated else y
+
+
+# ---------------------------------------------------------------------------------------- attention
+
+def qk_norm_rope_store(qkv, heads, kv_heads, head_dim, q_gain, k_gain, eps, cos_table, sin_table,
+                       tok_pos, tok_slot, block_table, k_store, v_store, write_cache=True):
+    """Norm and rotate the query and key heads of ``qkv`` and file keys and values in the cache.
+
+    ``qkv`` is ``[T, (heads + 2 * kv_heads) * head_dim]`` (queries alone,
+    ``[T, heads * head_dim]``, when ``write_cache`` is false); returns the queries
+    ``[T, heads * head_dim]``.  ``k_store``/``v_store`` are one cache entry's pages
+    ``[pages, kv_heads, 64, head_dim]``; ``block_table`` int32 ``[slots, max_pages]``.
+    """
+    _need(qkv, "qkv", None, 2)
+    n_tokens = qkv.shape[0]
+    width = (heads + 2 * kv_heads) * head_dim if write_cache else heads * head_dim
+    if qkv.shape[1] != width:
+        raise KernelError(f"qkv has width {qkv.shape[1]}, expected {width}")
+    if head_dim % 2 or head_dim > MAX_HEAD_DIM:
+        raise KernelError(f"head_dim {head_dim} must be even and at most {MAX_HEAD_DIM}")
+    _need(tok_pos, "tok_pos", torch.int32, 1)
+    _need(tok_slot, "tok_slot", torch.int32, 1)
+    _need(block_table, "block_table", torch.int32, 2)
+    gain_code = 0
+    for g in (q_gain, k_gain):
+        if g is not None:
+            _need(g, "head gain", None, 1)
+            if g.shape[0] != head_dim:
+                raise KernelError(f"head gain has {g.shape[0]} entries for head_dim {head_dim}")
+            gain_code = _gain_code(qkv, g)
+    if (q_gain is None) != (k_gain is None):
+        raise KernelError("q and k head norms come together")
+    if cos_table is not None:
+        _need(cos_table, "cos_table", torch.float32, 2)
+        _need(sin_table, "sin_table", torch.float32, 2)
+        if cos_table.shape[1] != head_dim // 2 or sin_table.shape != cos_table.shape:
+            raise KernelError("rotary tables must be [positions, head_dim / 2]")
+    if write_cache:
+        for store in (k_store, v_store):
+            _need(store, "cache pages", qkv.dtype, 4)
+            if tuple(store.shape[1:]) != (kv_heads, PAGE_TOKENS, head_dim):
+                raise KernelError(f"cache pages have shape {tuple(store.shape)}, expected "
+                                  f"[pages, {kv_heads}, {PAGE_TOKENS}, {head_dim}]")
+    q_out = torch.empty((n_tokens, heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    rc = build.load("rope_cache").sb_qk_norm_rope_store(
+        _code(qkv.dtype), gain_code, _ptr(qkv), _ptr(q_out), _ptr(q_gain), _ptr(k_gain),
+        _ptr(cos_table), _ptr(sin_table), _ptr(tok_pos), _ptr(tok_slot), _ptr(block_table),
+        block_table.shape[1], _ptr(k_store if write_cache else None),
+        _ptr(v_store if write_cache else None), n_tokens, heads, kv_heads, head_dim,
+        ctypes.c_float(eps), int(write_cache), qkv.shape[1], _stream())
+    _check(rc, "qk_norm_rope_store")
+    return q_out
+
+
+def attention_rowwise(q, k_store, v_store, block_table, tok_slot, tok_pos, heads, kv_heads, head_dim,
+                      scale, window=None):
+    """Causal attention of each query row over its sequence's cached keys (plain kernel)."""
+    _need(q, "q", None, 2)
+    if q.shape[1] != heads * head_dim:
+        raise KernelError(f"q has width {q.shape[1]}, expected {heads * head_dim}")
+    if head_dim > MAX_HEAD_DIM:
+        raise KernelError(f"head_dim {head_dim} exceeds {MAX_HEAD_DIM}")
+    if heads % kv_heads:
+        raise KernelError(f"{heads} query heads cannot share {kv_heads} key/value heads")
+    for store in (k_store, v_store):
+        _need(store, "cache pages", q.dtype, 4)
+        if tuple(store.shape[1:]) != (kv_heads, PAGE_TOKENS, head_dim):
+            raise KernelError(f"cache pages have shape {tuple(store.shape)}")
+    _need(block_table, "block_table", torch.int32, 2)
+    _need(tok_slot, "tok_slot", torch.int32, 1)
+    _need(tok_pos, "tok_pos", torch.int32, 1)
+    out = torch.empty_like(q)
+    rc = build.load("attention_rowwise").sb_attention_rowwise(
+        _code(q.dtype), _ptr(q), _ptr(out), _ptr(k_store), _ptr(v_store), _ptr(block_table),
+        block_table.shape[1], _ptr(tok_slot), _ptr(tok_pos), q.shape[0], heads, kv_heads, head_dim,
+        ctypes.c_float(scale), int(window or 0), _stream())
+    _check(rc, "attention_rowwise")
+    return out
+
+
+# ---------------------------------------------------------------------------------------- sampling
+
+def sample(logits, temperature=None, request_key=None, position=None, status=None, out=None):
+    """One token per row of float32 ``logits`` ``[B, V]``: argmax, or a draw where temperature > 0."""
+    _need(logits, "logits", torch.float32, 2)
+    rows, vocab = logits.shape
+    if temperature is not None:
+        _need(temperature, "temperature", torch.float32, 1)
+        _need(request_key, "request_key", torch.int32, 1)
+        _need(position, "position", torch.int32, 1)
+    if out is None:
+        out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    rc = build.load("sampling").sb_sample(
+        _ptr(logits), rows, vocab, ctypes.c_longlong(logits.stride(0)), _ptr(temperature),
+        _ptr(request_key), _ptr(position), _ptr(out), _ptr(status), _stream())
+    _check(rc, "sample")
+    return out

@@ -1,0 +1,46 @@
+"""Rotary position tables: cos and sin of ``position * theta ** (-2j / head_dim)``.
+
+The angles are formed in float32 exactly as the reference forms them
+(engine/engine.py:240-259): exponent ``arange(0, D, 2) / D``, ``inv_freq = 1 /
+theta ** exponent``, ``outer(position, inv_freq)``.  The two halves of the
+reference's ``[positions, D]`` table are equal, so only ``D / 2`` columns are kept.
+The tables stay float32; the kernel that applies them rounds to the working type
+where the reference casts (before any multiply).  Tables are computed on the host
+so that they are the same bits on every machine, and grow on demand.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .base import Part
+
+
+class RotaryTable(Part):
+    MIN_POSITIONS = 4096
+
+    def __init__(self, spec, dtype, device="cuda"):
+        super().__init__(spec, dtype)
+        self.device = device
+        self.length = 0
+        self.cos = None
+        self.sin = None
+
+    @staticmethod
+    def angles(theta: float, head_dim: int, length: int) -> torch.Tensor:
+        exponent = torch.arange(0, head_dim, 2, dtype=torch.int64).float() / head_dim
+        inv_freq = 1.0 / (theta ** exponent)
+        pos = torch.arange(length, dtype=torch.int64).float()
+        return torch.outer(pos, inv_freq)
+
+    def ensure(self, length: int) -> None:
+        """Make the tables cover positions ``[0, length)``."""
+        if length <= self.length:
+            return
+        size = max(self.MIN_POSITIONS, self.length)
+        while size < length:
+            size *= 2
+        freqs = self.angles(self.spec.theta, self.spec.head_dim, size)
+        self.cos = freqs.cos().contiguous().to(self.device)
+        self.sin = freqs.sin().contiguous().to(self.device)
+        self.length = size
