@@ -88,6 +88,10 @@ class ModelRunner:
     def close_sequence(self, slot: int) -> None:
         self.cache.close_sequence(slot)
 
+    def reserve(self, slot: int, tokens: int) -> None:
+        """Set pages aside so that ``slot`` can grow to ``tokens`` tokens without asking again."""
+        self.cache.reserve(slot, tokens)
+
     # ------------------------------------------------------------------ the step
 
     def make_context(self, entries) -> StepContext:

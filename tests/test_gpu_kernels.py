@@ -1,0 +1,247 @@
+"""Each CUDA kernel alone against a plain torch statement of the same op, at sizes other than the
+engine's, with inputs built so that a fault shows (a far key, a window's edge, a page's edge)."""
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+TOL = {"float32": dict(atol=2e-5, rtol=2e-5), "bfloat16": dict(atol=2e-2, rtol=2e-2)}
+
+
+def dev(t):
+    return t.to("cuda")
+
+
+def rand(*shape, dtype="float32", seed=0, scale=1.0):
+    gen = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=gen) * scale).to(DT[dtype])
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+def test_embedding_gathers_rows_and_flags_bad_ids(dtype):
+    from starter_b200 import ops
+
+    table = rand(37, 1000, dtype=dtype)
+    ids = torch.tensor([0, 36, 5, 5, 17], dtype=torch.int32)
+    out = ops.embedding(dev(ids), dev(table))
+    assert torch.equal(out.cpu(), table[ids.long()])
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = ops.embedding(dev(torch.tensor([3, 37], dtype=torch.int32)), dev(table), status)
+    assert status.item() == 1 and out[1].abs().sum().item() == 0
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("hidden", [24, 1000, 2560, 5121])
+def test_rmsnorm_alone_with_the_residual_sum_and_on_chosen_rows(dtype, hidden):
+    from starter_b200 import ops
+
+    x, d = rand(9, hidden, dtype=dtype, seed=1), rand(9, hidden, dtype=dtype, seed=2)
+    gain = (1 + 0.1 * rand(hidden, seed=3)).to(DT[dtype])
+    eps = 1e-5
+    want = plain.plain_rms_norm(x, gain, eps)
+    assert torch.allclose(ops.rmsnorm(dev(x), dev(gain), eps).cpu().float(), want.float(), **TOL[dtype])
+    total = x + d                                   # the sum is rounded to the working type, then normed
+    res = dev(x.clone())
+    got = ops.rmsnorm(res, dev(gain), eps, delta=dev(d))
+    assert torch.equal(res.cpu(), total)
+    assert torch.allclose(got.cpu().float(), plain.plain_rms_norm(total, gain, eps).float(), **TOL[dtype])
+    rows = torch.tensor([8, 0, 3], dtype=torch.int32)
+    res = dev(x.clone())
+    got = ops.rmsnorm(res, dev(gain), eps, delta=dev(d), rows=dev(rows))
+    assert torch.equal(res.cpu(), x)                # untouched
+    assert torch.allclose(got.cpu().float(), plain.plain_rms_norm(total[rows.long()], gain, eps).float(), **TOL[dtype])
+    if dtype == "bfloat16":                         # a gain stored in 32-bit stays 32-bit
+        got = ops.rmsnorm(dev(x), dev(gain.float()), eps)
+        assert torch.allclose(got.cpu().float(), want.float(), **TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+def test_swiglu(dtype):
+    from starter_b200 import ops
+
+    gu = rand(5, 2 * 311, dtype=dtype, seed=4, scale=3.0)
+    want = plain.plain_swiglu(gu[:, :311], gu[:, 311:])
+    assert torch.allclose(ops.swiglu(dev(gu)).cpu().float(), want.float(), **TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("rows,n,k", [(1, 7, 96), (2, 301, 100), (3, 64, 2560), (8, 33, 264), (16, 130, 1000),
+                                      (17, 70, 96), (130, 257, 77), (200, 1000, 264)])
+def test_linear_every_row_count_and_odd_sizes(dtype, rows, n, k):
+    from starter_b200 import ops
+
+    x, w = rand(rows, k, dtype=dtype, seed=5), rand(n, k, dtype=dtype, seed=6, scale=0.05)
+    want = x.double() @ w.double().t()
+    got = ops.linear(dev(x), dev(w))
+    assert got.dtype == DT[dtype]
+    assert torch.allclose(got.cpu().double(), want, **TOL[dtype])
+    got32 = ops.linear(dev(x), dev(w), out_float=True)
+    assert got32.dtype == torch.float32
+    assert torch.allclose(got32.cpu().double(), want, atol=2e-5 if dtype == "float32" else 2e-3, rtol=1e-3)
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("rows", [1, 5, 16, 40])
+def test_gated_linear_equals_product_then_swiglu(dtype, rows):
+    from starter_b200 import ops
+
+    inner, k = 150, 96
+    x, w = rand(rows, k, dtype=dtype, seed=7), rand(2 * inner, k, dtype=dtype, seed=8, scale=0.3)
+    gu = (x.double() @ w.double().t()).to(DT[dtype])
+    want = plain.plain_swiglu(gu[:, :inner], gu[:, inner:])
+    got = ops.linear(dev(x), dev(w), gated=True)
+    assert got.shape == (rows, inner)
+    assert torch.allclose(got.cpu().float(), want.float(), **TOL[dtype])
+
+
+def test_a_row_of_the_product_does_not_depend_on_the_other_rows():
+    from starter_b200 import ops
+
+    x, w = rand(16, 264, seed=9), rand(50, 264, seed=10)
+    full = ops.linear(dev(x), dev(w))
+    for rows in (1, 2, 5, 9):
+        assert torch.equal(ops.linear(dev(x[:rows]), dev(w)), full[:rows])
+
+
+def paged(keys, values, n_pages, order):
+    """File ``[T, kv_heads, D]`` keys and values of ONE sequence into pages chosen by ``order``."""
+    tokens, kv_heads, d = keys.shape
+    ks = torch.full((n_pages, kv_heads, 64, d), 7.0, dtype=keys.dtype)   # junk that must never be read
+    vs = torch.full((n_pages, kv_heads, 64, d), -7.0, dtype=keys.dtype)
+    for t in range(tokens):
+        ks[order[t // 64], :, t % 64] = keys[t]
+        vs[order[t // 64], :, t % 64] = values[t]
+    return ks, vs
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("heads,kv_heads,d", [(4, 2, 16), (6, 2, 48), (5, 5, 128), (8, 1, 256)])
+def test_qk_norm_rope_store_files_keys_at_each_tokens_own_place(dtype, heads, kv_heads, d):
+    from starter_b200 import ops
+
+    tokens, eps, theta = 11, 1e-5, 1e4
+    qkv = rand(tokens, (heads + 2 * kv_heads) * d, dtype=dtype, seed=11)
+    qg, kg = ((1 + 0.1 * rand(d, seed=s)).to(DT[dtype]) for s in (12, 13))
+    # two sequences: slot 2 continues at position 60 (crossing a page edge), slot 0 starts at 0
+    pos = torch.tensor([60, 61, 62, 63, 64, 65, 66, 0, 1, 2, 3], dtype=torch.int32)
+    slot = torch.tensor([2] * 7 + [0] * 4, dtype=torch.int32)
+    table = torch.tensor([[5, 0, 0], [0, 0, 0], [3, 1, 0]], dtype=torch.int32)
+    freqs = plain.plain_rope_tables(theta, d, 128, torch.float32)
+    cos32, sin32 = freqs[0][:, : d // 2].contiguous(), freqs[1][:, : d // 2].contiguous()
+    ks = torch.zeros(6, kv_heads, 64, d, dtype=DT[dtype], device="cuda")
+    vs = torch.zeros_like(ks)
+    q = ops.qk_norm_rope_store(dev(qkv), heads, kv_heads, d, dev(qg), dev(kg), eps, dev(cos32), dev(sin32),
+                               dev(pos), dev(slot), dev(table), ks, vs)
+    cos, sin = (t[pos.long()].to(DT[dtype]) for t in freqs)
+    q_in = qkv[:, : heads * d].view(tokens, heads, d)
+    k_in = qkv[:, heads * d:(heads + kv_heads) * d].view(tokens, kv_heads, d)
+    v_in = qkv[:, (heads + kv_heads) * d:].view(tokens, kv_heads, d)
+    q_want = plain.plain_apply_rope(plain.plain_rms_norm(q_in, qg, eps), cos, sin)
+    k_want = plain.plain_apply_rope(plain.plain_rms_norm(k_in, kg, eps), cos, sin)
+    assert torch.allclose(q.cpu().float().view(tokens, heads, d), q_want.float(), **TOL[dtype])
+    ks, vs = ks.cpu(), vs.cpu()
+    touched = torch.zeros(6, 64, dtype=torch.bool)
+    for t in range(tokens):
+        page = table[slot[t], pos[t] // 64].item()
+        off = pos[t].item() % 64
+        touched[page, off] = True
+        assert torch.allclose(ks[page, :, off].float(), k_want[t].float(), **TOL[dtype])
+        assert torch.equal(vs[page, :, off], v_in[t])
+    untouched = ~touched[:, None, :, None]
+    assert (ks * untouched).abs().sum().item() == 0 and (vs * untouched).abs().sum().item() == 0
+    # queries alone, nothing written
+    q2 = ops.qk_norm_rope_store(dev(qkv[:, : heads * d].contiguous()), heads, kv_heads, d, dev(qg), dev(kg), eps,
+                                dev(cos32), dev(sin32), dev(pos), dev(slot), dev(table), None, None,
+                                write_cache=False)
+    assert torch.equal(q2, q)
+
+
+def attention_case(dtype, heads, kv_heads, d, lengths, new, window, seed, spike=None):
+    """Sequences with ``lengths[i]`` cached tokens of which the last ``new[i]`` are this step's queries.
+    Returns what the kernel needs and the plain answer per query row."""
+    scale = d ** -0.5
+    n_pages, next_page = 40, 0
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(seed)).tolist()
+    ks = torch.full((n_pages, kv_heads, 64, d), 9.0, dtype=DT[dtype])
+    vs = torch.full((n_pages, kv_heads, 64, d), -9.0, dtype=DT[dtype])
+    table = torch.zeros(len(lengths), 8, dtype=torch.int32)
+    q_rows, slots, poss, wants = [], [], [], []
+    for s, (length, n) in enumerate(zip(lengths, new)):
+        k = rand(length, kv_heads, d, dtype=dtype, seed=seed + 3 * s)
+        v = rand(length, kv_heads, d, dtype=dtype, seed=seed + 3 * s + 1)
+        q = rand(length, heads, d, dtype=dtype, seed=seed + 3 * s + 2)
+        if spike is not None and spike < length:
+            # one far key must win for the last query: align them and make them large
+            k[spike] = (q[length - 1, :: heads // kv_heads][:kv_heads] * 4).to(DT[dtype])
+        for p in range((length + 63) // 64):
+            table[s, p] = perm[next_page]
+            next_page += 1
+        for t in range(length):
+            ks[table[s, t // 64], :, t % 64] = k[t]
+            vs[table[s, t // 64], :, t % 64] = v[t]
+        want = plain.plain_attention(q, k, v, scale, window)
+        for t in range(length - n, length):
+            q_rows.append(q[t].reshape(-1))
+            slots.append(s)
+            poss.append(t)
+            wants.append(want[t].reshape(-1))
+    return dict(q=torch.stack(q_rows), ks=ks, vs=vs, table=table,
+                slot=torch.tensor(slots, dtype=torch.int32), pos=torch.tensor(poss, dtype=torch.int32),
+                want=torch.stack(wants), scale=scale, q_start=None)
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("heads,kv_heads,d,window", [(4, 2, 16, None), (6, 2, 48, 5), (8, 8, 128, None),
+                                                    (8, 1, 64, 70), (3, 1, 256, None)])
+def test_attention_rowwise(dtype, heads, kv_heads, d, window):
+    from starter_b200 import ops
+
+    c = attention_case(dtype, heads, kv_heads, d, lengths=[130, 1, 64, 200], new=[130, 1, 3, 1],
+                       window=window, seed=20, spike=2)
+    got = ops.attention_rowwise(dev(c["q"]), dev(c["ks"]), dev(c["vs"]), dev(c["table"]), dev(c["slot"]),
+                                dev(c["pos"]), heads, kv_heads, d, c["scale"], window)
+    assert torch.allclose(got.cpu().float(), c["want"].float(), **TOL[dtype])
+
+
+def test_sampling_greedy_ties_and_seeded_draws():
+    from starter_b200 import ops
+    from starter_b200.sampling import gumbel_noise, request_key
+
+    logits = torch.zeros(3, 1000)
+    logits[0, [400, 7, 900]] = 2.0          # equal maxima: the lowest index wins
+    logits[1, 999] = 1.0
+    logits[2] = -1.0
+    logits[2, 0] = float("nan")
+    assert ops.sample(dev(logits)).tolist() == [7, 999, 1]
+    rows = rand(6, 5003, seed=30, scale=2.0)
+    temps = [0.0, 0.7, 1.5, 0.7, 0.0, 3.0]
+    keys = [request_key(9, i) for i in range(6)]
+    poss = [3, 3, 8, 4, 1, 0]
+    got = ops.sample(dev(rows), dev(torch.tensor(temps)), dev(torch.tensor(np.asarray(keys, dtype=np.uint32).view(np.int32))),
+                     dev(torch.tensor(poss, dtype=torch.int32))).tolist()
+    for i in range(6):
+        assert got[i] == plain.plain_select(rows[i].numpy(), temps[i], keys[i], poss[i])
+    nan = torch.full((1, 10), float("nan"))
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert ops.sample(dev(nan), status=status).tolist() == [0] and status.item() == 2
+
+
+def test_refusals_name_the_size():
+    from starter_b200 import ops
+
+    with pytest.raises(ops.KernelError, match="CUDA tensor"):
+        ops.rmsnorm(torch.zeros(2, 4), torch.ones(4), 1e-6)
+    with pytest.raises(ops.KernelError, match="head_dim"):
+        ops.attention_rowwise(dev(torch.zeros(1, 2 * 320)), dev(torch.zeros(1, 1, 64, 320)),
+                              dev(torch.zeros(1, 1, 64, 320)), dev(torch.zeros(1, 1, dtype=torch.int32)),
+                              dev(torch.zeros(1, dtype=torch.int32)), dev(torch.zeros(1, dtype=torch.int32)),
+                              2, 1, 320, 1.0)
+    with pytest.raises(ops.KernelError, match="contiguous"):
+        ops.linear(dev(torch.zeros(4, 8)).t(), dev(torch.zeros(3, 4)))
+    with pytest.raises(ops.KernelError, match="width"):
+        ops.linear(dev(torch.zeros(4, 8)), dev(torch.zeros(3, 9)))

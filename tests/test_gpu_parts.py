@@ -1,0 +1,181 @@
+"""Each layer part alone against the plain implementation, and a toy mixer with state of its own,
+defined here, registered, built and stepped without touching the library's files."""
+
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from gpu_helpers import DTYPES, assert_close, model_case
+from tiny import random_prompt
+
+pytestmark = pytest.mark.gpu
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def one_sequence_context(runner, n_tokens, slot=None):
+    from starter_b200.engine import StepEntry
+
+    slot = runner.open_sequence() if slot is None else slot
+    return slot, runner.make_context([StepEntry(slot, [0] * n_tokens, [])])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_parts_of_a_layer_one_by_one(tmp_path_factory, name, dtype):
+    from starter_b200.engine import ModelRunner, load_model
+
+    folder, cfg, w32 = model_case(tmp_path_factory, name)
+    w = {k: v.to(DT[dtype]) for k, v in w32.items()}
+    model = load_model(folder, dtype)
+    runner = ModelRunner(model, max_tokens=64 * 8, max_sequences=4)
+    layer = cfg["num_hidden_layers"] - 1          # in C this layer has a window
+    block = model.blocks[layer]
+    prefix = f"model.layers.{layer}."
+    tokens = 75
+    gen = torch.Generator().manual_seed(5)
+    x = torch.randn(tokens, cfg["hidden_size"], generator=gen).to(DT[dtype])
+    xd = x.cuda()
+
+    # norm
+    want = plain.plain_rms_norm(x, w[prefix + "input_layernorm.weight"], cfg["rms_norm_eps"])
+    assert_close(block.norm1(xd), want, dtype, "norm")
+    # position tables
+    d = plain.head_dim_of(cfg)
+    block.mixer.prepare(300)
+    cos, sin = plain.plain_rope_tables(cfg["rope_theta"], d, 301, torch.float32)
+    assert torch.equal(block.mixer.position.cos[:301].cpu(), cos[:, : d // 2])
+    assert torch.equal(block.mixer.position.sin[:301].cpu(), sin[:, : d // 2])
+    # feed-forward
+    assert_close(block.feed_forward(xd, None), plain.plain_feed_forward(x, w, prefix), dtype, "feed-forward")
+    # mixer: a whole sequence in one step, then the same sequence in two steps
+    cos_t, sin_t = plain.plain_rope_tables(cfg["rope_theta"], d, tokens, DT[dtype])
+    want = plain.plain_mixer(x, w, prefix, cfg, cos_t, sin_t, plain.layer_window(cfg, layer))
+    slot, ctx = one_sequence_context(runner, tokens)
+    assert_close(block.mixer(xd, ctx, layer, True), want, dtype, "mixer, whole")
+    runner.close_sequence(slot)
+    slot, ctx = one_sequence_context(runner, 70)
+    first = block.mixer(xd[:70].contiguous(), ctx, layer, True)
+    _, ctx = one_sequence_context(runner, 5, slot)
+    second = block.mixer(xd[70:].contiguous(), ctx, layer, True)
+    assert_close(torch.cat([first, second]), want, dtype, "mixer, 70 + 5")
+    runner.close_sequence(slot)
+    # the whole block
+    slot, ctx = one_sequence_context(runner, tokens)
+    residual, pending = block(xd.clone(), None, ctx, layer, True)
+    cfg_one = dict(cfg)
+    want = plain.plain_block(x, w, layer, cfg_one, cos_t, sin_t)
+    assert_close((residual.float() + pending.float()), want, dtype, "block")
+    runner.close_sequence(slot)
+
+
+# ----------------------------------------------------------------------------- a toy mixer with state
+
+@dataclass(frozen=True)
+class RunningMeanSpec:
+    hidden_size: int
+    kind: str = "toy_running_mean"
+
+
+class RunningMeanMixer:
+    """y_t = W . mean(x_0 .. x_t): needs no keys, only a running sum and a count per sequence."""
+
+    def __init__(self, spec, dtype, position=None):
+        self.spec, self.dtype = spec, dtype
+
+    def param_specs(self):
+        from starter_b200.parts import ParamSpec
+        return {"w": ParamSpec((self.spec.hidden_size, self.spec.hidden_size))}
+
+    def set_params(self, params):
+        self.w = params["w"]
+
+    def kv_need(self):
+        return None
+
+    def state_need(self):
+        from starter_b200.cache import StateNeed
+        return StateNeed((self.spec.hidden_size + 1,), "float32")
+
+    def prepare(self, max_position):
+        pass
+
+    def weight_bytes(self):
+        return self.w.numel() * self.w.element_size()
+
+    def __call__(self, x, ctx, entry, writes_cache=True):
+        state = ctx.cache.entry_state(entry)
+        h = self.spec.hidden_size
+        means = torch.empty_like(x, dtype=torch.float32)
+        for slot, start, n in zip(ctx.host["seq_slot"].tolist(), ctx.host["seq_q_start"].tolist(),
+                                  ctx.host["seq_q_len"].tolist()):
+            rows = x[start:start + n].float()
+            sums = state[slot, :h] + rows.cumsum(0)
+            counts = state[slot, h] + torch.arange(1, n + 1, device=x.device)
+            means[start:start + n] = sums / counts[:, None]
+            state[slot, :h] = sums[-1]
+            state[slot, h] = counts[-1]
+        return (means.to(x.dtype) @ self.w.t())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_toy_mixer_with_state_registers_builds_and_steps(dtype):
+    from starter_b200.config import (GatedFeedForwardSpec, LayerSpec, ModelSpec, NormSpec, RopeSpec,
+                                     AttentionSpec, ScheduleEntry)
+    from starter_b200.engine import DecoderModel, ModelRunner, StepEntry
+    from starter_b200.parts import register
+    from starter_b200.weights import random_checkpoint
+
+    register("mixer", "toy_running_mean", RunningMeanMixer)
+    hidden, vocab = 48, 101
+    norm = NormSpec(hidden, 1e-5)
+    ff = GatedFeedForwardSpec(hidden, 80)
+    attn = AttentionSpec(hidden, 3, 1, 16, 0.25, True, 1e-5, RopeSpec(16, 1e4))
+
+    def names(i, mixer_names):
+        out = {"norm1.weight": f"l{i}.n1", "norm2.weight": f"l{i}.n2", "feed_forward.gate": f"l{i}.gate",
+               "feed_forward.up": f"l{i}.up", "feed_forward.down": f"l{i}.down"}
+        out.update({f"mixer.{k}": f"l{i}.{k}" for k in mixer_names})
+        return out
+
+    layers = (
+        LayerSpec(RunningMeanSpec(hidden), ff, norm, norm, names(0, ["w"])),
+        LayerSpec(attn, ff, norm, norm, names(1, ["q", "k", "v", "o", "q_norm", "k_norm"])),
+    )
+    # run order: toy, attention, toy again (its weights shared, a state of its own), and attention
+    # once more reading the keys its first run wrote
+    schedule = (ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(0, 2), ScheduleEntry(1, 1, writes_cache=False))
+    spec = ModelSpec("Toy", vocab, hidden, layers, schedule, norm, True, "embed", "final", "head")
+    model = DecoderModel(spec, DT[dtype], "cuda")
+    tensors = random_checkpoint(model.expected_tensors(), 3, DT[dtype], "cuda")
+    model.load_tensors(tensors)
+    assert model.kv_needs()[0] is None and model.kv_needs()[1] is not None
+    runner = ModelRunner(model, max_tokens=64 * 8, max_sequences=4)
+    assert set(runner.cache.state) == {0, 2} and len(runner.cache.groups) == 1
+
+    a, b = random_prompt(70, vocab, 1), random_prompt(9, vocab, 2)
+    sa, sb = runner.open_sequence(), runner.open_sequence()
+    whole = runner.step([StepEntry(sa, a, list(range(70))), StepEntry(sb, b, list(range(9)))])
+    runner.close_sequence(sa)
+    runner.close_sequence(sb)
+    # the same two requests cut differently, in slots that were just used: state must start at zero
+    sb, sa = runner.open_sequence(), runner.open_sequence()
+    rows_a = [runner.step([StepEntry(sa, a[:66], list(range(66)))])]
+    rows_b = []
+    for i in range(4):
+        out = runner.step([StepEntry(sa, [a[66 + i]], [0]), StepEntry(sb, b[2 * i:2 * i + 2], [0, 1])])
+        rows_a.append(out[:1])
+        rows_b.append(out[1:])
+    rows_b.append(runner.step([StepEntry(sb, b[8:], [0])]))
+    assert_close(torch.cat(rows_a + rows_b), whole, dtype, "toy model, cut in steps")
+    # and the toy layer does what it says: compare its first run with plain torch
+    x = model.embed[torch.tensor(b, device="cuda")].float()
+    n1 = plain.plain_rms_norm(x.to(DT[dtype]).cpu(), tensors["l0.n1"].cpu(), 1e-5).float()
+    means = n1.cumsum(0) / torch.arange(1, 10)[:, None]
+    want = means.to(DT[dtype]) @ tensors["l0.w"].cpu().t()
+    s = runner.open_sequence()
+    ctx = runner.make_context([StepEntry(s, b, [])])
+    got = model.blocks[0].mixer(model.blocks[0].norm1(model.embed[torch.tensor(b, device="cuda")].contiguous()), ctx, 0, True)
+    assert_close(got, want, dtype, "toy mixer alone")

@@ -1,0 +1,92 @@
+"""The plain implementation itself (no GPU): held against the reference's own code once, and
+checked for the properties the engine tests rely on."""
+
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from tiny import TINY, make_folder, random_prompt
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "reference_logits.json")
+
+
+def test_plain_matches_reference_code(tmp_path):
+    """tests/golden/reference_logits.json holds logits computed by the reference's engine/engine.py
+    on the CPU (see tests/golden/make_golden.py)."""
+    cases = json.load(open(GOLDEN))["cases"]
+    assert len(cases) >= 3
+    for case in cases:
+        folder = make_folder(tmp_path, case["config"], seed=case["seed"], **case["overrides"])
+        cfg, w = plain.read_model_folder(folder)
+        got = plain.plain_forward(cfg, w, case["prompt"])
+        want = torch.tensor(case["logits"], dtype=torch.float32)
+        assert got.shape == want.shape
+        assert (got - want).abs().max().item() < 2e-6
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_a_position_sees_only_its_past(tmp_path, name):
+    folder = make_folder(tmp_path, name, seed=1)
+    cfg, w = plain.read_model_folder(folder)
+    prompt = random_prompt(20, cfg["vocab_size"], 3)
+    full = plain.plain_forward(cfg, w, prompt)
+    part = plain.plain_forward(cfg, w, prompt[:11])
+    assert (full[:11] - part).abs().max().item() < 1e-5
+    changed = list(prompt)
+    changed[15] = (changed[15] + 1) % cfg["vocab_size"]
+    other = plain.plain_forward(cfg, w, changed)
+    assert torch.equal(other[:15], full[:15]) and not torch.equal(other[15:], full[15:])
+
+
+def test_window_hides_keys_further_back_than_its_size():
+    torch.manual_seed(0)
+    q, k, v = torch.randn(12, 2, 8), torch.randn(12, 1, 8), torch.randn(12, 1, 8)
+    full = plain.plain_attention(q, k, v, 0.3)
+    win = plain.plain_attention(q, k, v, 0.3, window=4)
+    assert torch.allclose(full[:4], win[:4], atol=1e-6)          # the first 4 queries see the same keys
+    assert not torch.allclose(full[6:], win[6:], atol=1e-4)
+    # query 9 with window 4 sees keys 6..9 only: changing key 5 changes nothing, key 6 does
+    k2 = k.clone(); k2[5] += 3
+    assert torch.equal(plain.plain_attention(q, k2, v, 0.3, window=4)[9], win[9])
+    k3 = k.clone(); k3[6] += 3
+    assert not torch.equal(plain.plain_attention(q, k3, v, 0.3, window=4)[9], win[9])
+
+
+def test_grouped_heads_share_keys_in_blocks():
+    torch.manual_seed(1)
+    q, k, v = torch.randn(5, 6, 4), torch.randn(5, 2, 4), torch.randn(5, 2, 4)
+    out = plain.plain_attention(q, k, v, 0.5)
+    for h in range(6):
+        alone = plain.plain_attention(q[:, h:h + 1], k[:, h // 3:h // 3 + 1], v[:, h // 3:h // 3 + 1], 0.5)
+        assert torch.allclose(out[:, h], alone[:, 0], atol=1e-6)
+
+
+def test_rms_norm_rope_and_swiglu_formulas():
+    x = torch.tensor([[3.0, 4.0]])
+    assert torch.allclose(plain.plain_rms_norm(x, torch.tensor([2.0, 0.5]), 0.0),
+                          torch.tensor([[2 * 3 / 12.5 ** 0.5, 0.5 * 4 / 12.5 ** 0.5]]))
+    cos, sin = plain.plain_rope_tables(10000.0, 4, 3, torch.float32)
+    assert torch.allclose(cos[0], torch.ones(4)) and torch.allclose(sin[0], torch.zeros(4))
+    assert cos[2, 0].item() == pytest.approx(np.cos(2.0), rel=1e-6)
+    assert cos[2, 1].item() == pytest.approx(np.cos(2.0 / 100.0), rel=1e-6)
+    v = torch.tensor([[[1.0, 2.0, 3.0, 4.0]]])
+    r = plain.plain_apply_rope(v, cos[1:2], sin[1:2])[0, 0]
+    c0, s0, c1, s1 = np.cos(1.0), np.sin(1.0), np.cos(0.01), np.sin(0.01)
+    assert torch.allclose(r, torch.tensor([1 * c0 - 3 * s0, 2 * c1 - 4 * s1, 3 * c0 + 1 * s0, 4 * c1 + 2 * s1],
+                                          dtype=torch.float32), atol=1e-6)
+    g, u = torch.tensor([1.5, -2.0]), torch.tensor([2.0, 3.0])
+    assert torch.allclose(plain.plain_swiglu(g, u), g / (1 + torch.exp(-g)) * u)
+
+
+def test_greedy_takes_the_lowest_of_equal_maxima_and_draws_are_seeded():
+    assert plain.plain_select([1.0, 3.0, 3.0, 2.0], 0.0) == 1
+    row = np.linspace(-1, 1, 40).astype(np.float32)
+    a = plain.plain_select(row, 0.8, plain.plain_request_key(3, 1), 9)
+    assert a == plain.plain_select(row, 0.8, plain.plain_request_key(3, 1), 9)
+    from starter_b200.sampling import gumbel_noise, request_key
+    assert plain.plain_request_key(3, 1) == request_key(3, 1)
+    assert np.array_equal(plain.plain_gumbel(77, 4, 33), gumbel_noise(77, 4, 33))
