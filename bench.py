@@ -1,0 +1,260 @@
+"""Decode and prefill throughput of starter_b200 at Qwen3-4B size on ONE B200, random weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+
+Prints one JSON line.  A "step" is one decode step of the whole batch.  ``value`` is decoded
+tokens per second at batch 8, timed on the device with CUDA events around K consecutive steps of
+the captured, self-feeding decode step at the middle of the generation range (context 3,072 of
+4,096); ``e2e`` is the same through ``Engine.generate`` with host token ids in and out every step;
+``prefill`` is one 2,048-token prompt; ``points`` are decode at batch 1 and 64; ``roofline`` sets the
+bytes a decode step must read (every weight it uses once, the live requests' keys and values)
+against the measured copy bandwidth.  Every step reads >8 GB of weights, far more than the 126 MB
+L2, so nothing is flushed between steps.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_4B = dict(
+    architectures=["Qwen3ForCausalLM"], num_hidden_layers=36, hidden_size=2560, num_attention_heads=32,
+    num_key_value_heads=8, head_dim=128, intermediate_size=9728, vocab_size=151936, rope_theta=5e6,
+    rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=4096,
+)
+CONTEXT = 4096
+PROMPT = 2048
+DECODE_AT = 3072  # 2,048 prompt tokens + 1,024 decoded: the middle of the generation range
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    out = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    if os.path.isfile(path):
+        try:
+            raw = json.load(open(path))
+            out["hbm_gbs"] = float(raw.get("hbm_gbs", out["hbm_gbs"]))
+            out["bf16_tflops"] = float(raw.get("bf16_tflops", out["bf16_tflops"]))
+            out["source"] = "measured"
+        except Exception:  # noqa: BLE001
+            pass
+    return out
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed regions run."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.monotonic(), line.strip()))
+
+    def stop(self, windows):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        clocks, max_clock, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for stamp, line in self.samples:
+            if not any(a <= stamp <= b for a, b in windows):
+                continue
+            parts = [p.strip() for p in line.split(",")]
+            try:
+                clocks.append(int(parts[0]))
+                max_clock = int(parts[1])
+            except (ValueError, IndexError):
+                continue
+            for name, flag in zip(names, parts[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        clocks.sort()
+        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None, "sm_max_mhz": max_clock,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def reference_arm():
+    # The reference is a folder of scripts without packaging metadata, so pip has nothing to install;
+    # its Engine loads weights through a model library whose installed version lacks the attribute
+    # it reads (engine/engine.py:146), and its kernels are Triton.  Recorded in DESIGN.md.
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "alvinyuwen/starter has no setup.py/pyproject (pip install fails) and its "
+                      "Engine needs transformers==4.51.3 (config.rope_theta) which is not installed"}))
+    return 0
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--layers", type=int, default=QWEN3_4B["num_hidden_layers"],
+                        help="fewer layers than the model has (both numbers are reported)")
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU: this library has no multi-GPU path (asked for {args.gpus})")
+        return 2
+    warmup = max(args.warmup, 3)
+    steps = max(args.steps, 1)
+
+    import torch
+
+    from starter_b200 import ops
+    from starter_b200.config import config_from_dict
+    from starter_b200.engine import ModelRunner, StepEntry, random_model
+    from starter_b200.engine.entry import Engine
+
+    raw = dict(QWEN3_4B, num_hidden_layers=args.layers)
+    config = config_from_dict(raw)
+    model = random_model(config, seed=0, dtype="bfloat16")
+    vocab = config.vocab_size
+    pk = peaks()
+    sampler = ClockSampler()
+    sampler.start()
+    windows = []
+    gen = torch.Generator().manual_seed(0)
+
+    def prompt(n):
+        return torch.randint(0, vocab, (n,), generator=gen).tolist()
+
+    max_batch = max(args.batch, 1 if args.skip_points else 64)
+    runner = ModelRunner(model, max_tokens=max_batch * CONTEXT, max_sequences=max_batch)
+
+    def timed(fn, reps):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        t0 = time.monotonic()
+        start.record()
+        for _ in range(reps):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        windows.append((t0, time.monotonic()))
+        return start.elapsed_time(stop) / reps
+
+    # ---------------------------------------------------------------- prefill of 2,048 tokens
+    def prefill_once():
+        slot = runner.open_sequence()
+        runner.step([StepEntry(slot, prefill_prompt, [PROMPT - 1])])
+        runner.close_sequence(slot)
+
+    prefill_prompt = prompt(PROMPT)
+    for _ in range(warmup):
+        prefill_once()
+    prefill_ms = timed(prefill_once, 5)
+    h, nh, kv, d, inter, layers = (config.hidden_size, config.num_attention_heads,
+                                   config.num_key_value_heads, config.head_dim,
+                                   config.intermediate_size, args.layers)
+    per_token = 2 * h * (nh + 2 * kv) * d + 2 * nh * d * h + 2 * h * 2 * inter + 2 * inter * h
+    attn = 4 * nh * d * PROMPT * (PROMPT + 1) / 2
+    prefill_flops = layers * (per_token * PROMPT + attn) + 2 * h * vocab
+    prefill = {"value": round(PROMPT / prefill_ms * 1e3, 1), "tokens": PROMPT, "ms": round(prefill_ms, 3),
+               "frac": round(prefill_flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    # ---------------------------------------------------------------- decode, device-timed
+    def decode_point(batch):
+        slots = [runner.open_sequence() for _ in range(batch)]
+        for s in slots:
+            runner.reserve(s, CONTEXT)
+            runner.step([StepEntry(s, prompt(DECODE_AT), [])])
+        entries = [StepEntry(s, [1], [0]) for s in slots]
+        zeros = [0.0] * batch
+        keys = [0] * batch
+
+        def one():
+            runner.decode_tokens(entries, zeros, keys)
+
+        for _ in range(warmup):
+            one()
+        before = ops.launch_count
+        ms = timed(one, steps)
+        per_graph = runner.graphs.kernels_per_replay.get(batch, 0)
+        launches = steps * per_graph + (ops.launch_count - before)
+        for s in slots:
+            runner.close_sequence(s)
+        kv_bytes = runner.cache.bytes_per_token() * batch * (DECODE_AT + warmup + steps / 2)
+        return ms, launches, model.step_weight_bytes() + kv_bytes
+
+    ms, launches, step_bytes = decode_point(args.batch)
+    value = args.batch / ms * 1e3
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            b_ms, _, _ = decode_point(b)
+            points[f"decode_b{b}"] = round(b / b_ms * 1e3, 1)
+
+    # ---------------------------------------------------------------- end to end through Engine.generate
+    del runner
+    torch.cuda.empty_cache()
+    engine = Engine.from_model(model, max_batch=args.batch)
+    e2e_prompts = [prompt(DECODE_AT) for _ in range(args.batch)]
+    stream = engine.generate(e2e_prompts, warmup + steps + 1)
+    for _ in range(warmup + 1):
+        next(stream)
+    torch.cuda.synchronize()
+    t0 = time.monotonic()
+    for _ in range(steps):
+        next(stream)
+    torch.cuda.synchronize()
+    t1 = time.monotonic()
+    windows.append((t0, t1))
+    stream.close()
+    e2e_value = args.batch * steps / (t1 - t0)
+
+    clocks = sampler.stop(windows)
+    line = {
+        "metric": "decode tok/s at batch 8 (Qwen3-4B BF16); prefill tok/s at 2,048 tokens; batch 1/64 in points",
+        "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random weights N(0,0.02), uniform random token ids",
+        "config": {
+            "model": "Qwen3-4B", "layers": args.layers, "layers_of_model": QWEN3_4B["num_hidden_layers"],
+            "hidden": h, "heads": nh, "kv_heads": kv, "head_dim": d, "intermediate": inter, "vocab": vocab,
+            "tied": True, "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT,
+            "decode_context": DECODE_AT, "parallelism": "single", "l2": "inputs larger than L2",
+            "cache_page": 64, "peaks": pk["source"],
+        },
+        "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 4 * args.batch},
+        "gpu_launches": launches,
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clocks,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

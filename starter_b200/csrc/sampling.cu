@@ -21,8 +21,8 @@ __host__ __device__ __forceinline__ uint32_t sb_mix32(uint32_t x) {
 __global__ void sample_kernel(const float* __restrict__ logits, int vocab, size_t row_stride,
                               const float* __restrict__ temperature,
                               const uint32_t* __restrict__ request_key,
-                              const int* __restrict__ position, int* __restrict__ out,
-                              int* status) {
+                              const int* position, int* __restrict__ out,
+                              int* status, int* feed_token, int* feed_pos, int* feed_len) {
   __shared__ float best_v[32];
   __shared__ int best_i[32];
   const int row = blockIdx.x;
@@ -69,6 +69,13 @@ __global__ void sample_kernel(const float* __restrict__ logits, int vocab, size_
         bi = 0;
       }
       out[row] = bi;
+      // self-feeding decode: the drawn token becomes the row's next input, one position further on
+      // (engine/engine.py:835-838).  Every thread read position[row] before the barrier above.
+      if (feed_token) {
+        feed_token[row] = bi;
+        feed_pos[row] += 1;
+        feed_len[row] += 1;
+      }
     }
   }
 }
@@ -77,14 +84,15 @@ extern "C" {
 
 // logits: [rows, vocab] float with `row_stride` floats between rows.  temperature may be null (all
 // greedy); rows with temperature <= 0 are greedy.  request_key and position are read only for rows
-// that draw.
+// that draw.  With feed_token (all three feed arrays or none), row r also stores its token in
+// feed_token[r] and adds one to feed_pos[r] and feed_len[r]; position may alias feed_len.
 int sb_sample(const float* logits, int rows, int vocab, long long row_stride, const float* temperature,
               const uint32_t* request_key, const int* position, int* out, int* status,
-              cudaStream_t s) {
+              int* feed_token, int* feed_pos, int* feed_len, cudaStream_t s) {
   if (rows == 0) return 0;
   const int threads = vocab >= 8192 ? 1024 : 256;
   sample_kernel<<<rows, threads, 0, s>>>(logits, vocab, (size_t)row_stride, temperature, request_key,
-                                         position, out, status);
+                                         position, out, status, feed_token, feed_pos, feed_len);
   return SB_LAUNCH_RESULT();
 }
 

@@ -1,6 +1,6 @@
 from .batch import StepContext, StepEntry, plan_step
 from .model import DecoderModel, expected_tensors
-from .runner import ModelRunner, load_model, resolve_dtype
+from .runner import ModelRunner, load_model, random_model, resolve_dtype
 
 __all__ = ["DecoderModel", "ModelRunner", "StepContext", "StepEntry", "expected_tensors",
-           "load_model", "plan_step", "resolve_dtype"]
+           "load_model", "plan_step", "random_model", "resolve_dtype"]

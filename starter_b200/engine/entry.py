@@ -32,6 +32,18 @@ class Engine:
             self._build_runner(max_tokens)
         print(f"[engine] loaded {len(self.model.blocks)} layers as {self.model.dtype}", flush=True)
 
+    @classmethod
+    def from_model(cls, model, max_batch: int = 64, max_tokens: int | None = None) -> "Engine":
+        """An engine around a model that is already on the device (for instance random weights)."""
+        self = cls.__new__(cls)
+        self.model = model
+        self.max_batch = max_batch
+        self.runner = None
+        self._fixed_tokens = max_tokens
+        if max_tokens is not None:
+            self._build_runner(max_tokens)
+        return self
+
     def _build_runner(self, max_tokens: int) -> None:
         self.runner = None
         torch.cuda.empty_cache()

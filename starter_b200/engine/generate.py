@@ -108,12 +108,13 @@ class GenerationLoop:
             entries = [StepEntry(slots[i], list(requests[i].prompt), [len(requests[i].prompt) - 1])
                        for i in active]
             while active:
-                logits = runner.step(entries)
-                drawn = self.sampler.select(
-                    logits,
-                    [requests[i].sampling.temperature for i in active],
-                    [keys[i] for i in active],
-                    [lengths[i] for i in active])
+                temps = [requests[i].sampling.temperature for i in active]
+                now_keys = [keys[i] for i in active]
+                places = [lengths[i] for i in active]
+                if hasattr(runner, "step_and_select"):
+                    drawn = runner.step_and_select(entries, self.sampler, temps, now_keys, places)
+                else:
+                    drawn = self.sampler.select(runner.step(entries), temps, now_keys, places)
                 step_out = {}
                 still = []
                 for i, tok in zip(active, drawn):

@@ -1,0 +1,108 @@
+"""The single-token step captured in CUDA graphs, one per batch size, self-feeding.
+
+A decode step at small batch is hundreds of short kernels; launched one by one the
+host is the bottleneck (engine/engine.py:9-12).  The step for ``B`` sequences reads
+everything that changes from fixed device buffers (each row's token, position,
+slot, length and sampling settings) so one capture serves every step
+(engine/engine.py:805-809, 1029-1059).  The sampling kernel writes the drawn token
+back as the row's next input and advances its position, so consecutive steps of an
+unchanged batch need no host-to-device traffic at all (engine/engine.py:835-838).
+Unlike the reference, lengths are per row, and a batch that shrinks simply uses
+the graph of the smaller size.
+
+The graph runs the same model code and kernels as the eager step; it is captured
+the first time a batch size is used.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from .. import ops
+from .batch import StepContext
+
+
+class DecodeGraphs:
+    def __init__(self, runner, max_batch: int):
+        self.runner = runner
+        self.max_batch = max_batch
+        dev = runner.device
+        # one int32 buffer holds every per-row field, so one copy refreshes a batch
+        self.fields = ("tokens", "tok_pos", "tok_slot", "kv_len", "temperature", "key")
+        self.meta = torch.zeros((len(self.fields), max_batch), dtype=torch.int32, device=dev)
+        self.rows = torch.arange(max_batch, dtype=torch.int32, device=dev)
+        self.ones = torch.ones(max_batch, dtype=torch.int32, device=dev)
+        self.out = torch.zeros(max_batch, dtype=torch.int32, device=dev)
+        self.graphs = {}
+        self.logits = {}
+        self.kernels_per_replay = {}  # this library's kernels inside each graph
+        self.fed = None  # the slots whose next inputs the device already holds
+
+    def _field(self, name, batch):
+        return self.meta[self.fields.index(name), :batch]
+
+    def context(self, batch: int) -> StepContext:
+        return StepContext(
+            n_tokens=batch, n_seqs=batch,
+            tokens=self._field("tokens", batch), tok_pos=self._field("tok_pos", batch),
+            tok_slot=self._field("tok_slot", batch), seq_slot=self._field("tok_slot", batch),
+            seq_q_start=self.rows[:batch], seq_q_len=self.ones[:batch],
+            seq_kv_len=self._field("kv_len", batch), want_rows=self.rows[:batch],
+            max_q_len=1, max_kv_len=0, cache=self.runner.cache, status=self.runner.status, host=None)
+
+    def _body(self, batch: int):
+        model = self.runner.model
+        ctx = self.context(batch)
+        logits = model.forward(ctx, ctx.want_rows)
+        ops.sample(logits, self._field("temperature", batch).view(torch.float32),
+                   self._field("key", batch), self._field("kv_len", batch),
+                   status=self.runner.status, out=self.out[:batch],
+                   feed=(self._field("tokens", batch), self._field("tok_pos", batch),
+                         self._field("kv_len", batch)))
+        return logits
+
+    def _capture(self, batch: int) -> None:
+        saved = self.meta.clone()
+        # warm up on a side stream (compiles kernels, sizes library workspaces), then capture;
+        # both run the real step, so the fields are restored afterwards and the cache rows the
+        # warm-up wrote are rewritten by the real step before they are ever read
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self.meta.copy_(saved)
+                self._body(batch)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.meta.copy_(saved)
+        graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count
+        with torch.cuda.graph(graph):
+            self.logits[batch] = self._body(batch)
+        self.kernels_per_replay[batch] = ops.launch_count - before
+        self.graphs[batch] = graph
+        self.meta.copy_(saved)
+        torch.cuda.synchronize()
+
+    def load(self, slots, tokens, positions, temperatures, keys) -> None:
+        """Put a batch's rows on the device (one copy)."""
+        batch = len(slots)
+        host = np.zeros((len(self.fields), batch), dtype=np.int32)
+        host[0] = tokens
+        host[1] = positions
+        host[2] = slots
+        host[3] = np.asarray(positions, dtype=np.int32) + 1
+        host[4] = np.asarray(temperatures, dtype=np.float32).view(np.int32)
+        host[5] = np.asarray(keys, dtype=np.uint32).view(np.int32)
+        pinned = torch.from_numpy(host).pin_memory()
+        self.meta[:, :batch].copy_(pinned, non_blocking=True)
+        self.fed = tuple(slots)
+
+    def replay(self, batch: int) -> torch.Tensor:
+        """Run one step for the ``batch`` rows on the device; returns the drawn tokens (device)."""
+        if batch not in self.graphs:
+            self._capture(batch)
+        self.graphs[batch].replay()
+        return self.out[:batch]

@@ -20,6 +20,7 @@ from ..cache import SequenceCache
 from ..config import load_config
 from ..weights import load_checkpoint
 from .batch import StepContext, StepEntry, plan_step, upload
+from .graphs import DecodeGraphs
 from .model import DecoderModel
 
 DTYPES = {
@@ -68,9 +69,22 @@ def load_model(model_dir: str, dtype="bfloat16", device="cuda:0") -> DecoderMode
     return model
 
 
+def random_model(config, seed: int, dtype="bfloat16", device="cuda:0") -> DecoderModel:
+    """The model of ``config`` (a typed config) with random weights drawn on the device: no disk.
+    (Values differ from a model folder written with the same seed, which is drawn on the CPU.)"""
+    from ..weights import random_checkpoint
+
+    device = require_cuda(device)
+    dtype = resolve_dtype(dtype)
+    model = DecoderModel(config.to_model_spec(), dtype, device)
+    model.load_tensors(random_checkpoint(model.expected_tensors(), seed, dtype, device))
+    model.config = config
+    return model
+
+
 class ModelRunner:
     def __init__(self, model: DecoderModel, max_tokens: int, max_sequences: int | None = None,
-                 max_sequence_tokens: int | None = None):
+                 max_sequence_tokens: int | None = None, use_graphs: bool = True):
         self.model = model
         self.device = model.device
         pages = (max_tokens + 63) // 64
@@ -79,6 +93,8 @@ class ModelRunner:
         self.cache = SequenceCache(model.kv_needs(), model.state_needs(), max_tokens, max_sequences,
                                    model.dtype, self.device, max_sequence_tokens)
         self.status = torch.zeros((1,), dtype=torch.int32, device=self.device)
+        self.graphs = DecodeGraphs(self, max_sequences) if use_graphs else None
+        self.launches = 0
 
     # ------------------------------------------------------------------ sequences
 
@@ -118,8 +134,40 @@ class ModelRunner:
     def step(self, entries) -> torch.Tensor:
         """Run one step; ``entries`` is a list of ``StepEntry``.  Returns ``[wanted, vocab]`` float32."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        if self.graphs is not None:
+            self.graphs.fed = None
         ctx = self.make_context(entries)
         return self.model.forward(ctx, ctx.want_rows)
+
+    @torch.inference_mode()
+    def step_and_select(self, entries, sampler, temperatures, keys, positions) -> list:
+        """One step plus token selection (the logits wanted are each entry's last place).
+
+        Steps in which every sequence brings one token run as a captured graph that feeds itself;
+        anything else runs the eager step and the sampler.  Both run the same kernels."""
+        single = self.graphs is not None and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+        if not single:
+            return sampler.select(self.step(entries), temperatures, keys, positions)
+        return self.decode_tokens(entries, temperatures, keys).tolist()
+
+    @torch.inference_mode()
+    def decode_tokens(self, entries, temperatures, keys) -> torch.Tensor:
+        """Graph path of ``step_and_select``; returns the drawn tokens on the device."""
+        cache, graphs = self.cache, self.graphs
+        slots = tuple(e.slot for e in entries)
+        for e in entries:
+            cache.reserve(e.slot, cache.lengths[e.slot] + 1)
+        if graphs.fed != slots:
+            for e in entries:
+                if not 0 <= e.tokens[0] < self.model.spec.vocab_size:
+                    raise ValueError(f"token id {e.tokens[0]} is outside the vocabulary")
+            graphs.load(slots, [e.tokens[0] for e in entries], [cache.lengths[s] for s in slots],
+                        temperatures, keys)
+        for s in slots:
+            cache.advance(s, 1)
+        cache.sync_table()
+        self.model.prepare(max(cache.lengths[s] for s in slots))
+        return graphs.replay(len(slots))
 
     def check_status(self) -> None:
         """Raise if a kernel flagged a bad input since the last check (reads one int from the device)."""

@@ -51,7 +51,13 @@ def _need(t, name, dtype=None, ndim=None):
         raise KernelError(f"{name} must have {ndim} dimensions, got shape {tuple(t.shape)}")
 
 
+#: how many kernels of this library have been launched by this process (library GEMMs not counted)
+launch_count = 0
+
+
 def _check(rc, what):
+    global launch_count
+    launch_count += 1
     if rc != 0:
         if rc == -1:
             raise KernelError(f"{what}: this combination of dtypes has no kernel")
@@ -245,8 +251,11 @@ def attention_rowwise(q, k_store, v_store, block_table, tok_slot, tok_pos, heads
 
 # ---------------------------------------------------------------------------------------- sampling
 
-def sample(logits, temperature=None, request_key=None, position=None, status=None, out=None):
-    """One token per row of float32 ``logits`` ``[B, V]``: argmax, or a draw where temperature > 0."""
+def sample(logits, temperature=None, request_key=None, position=None, status=None, out=None, feed=None):
+    """One token per row of float32 ``logits`` ``[B, V]``: argmax, or a draw where temperature > 0.
+
+    ``feed = (tokens, positions, lengths)`` (int32 ``[B]`` each): the drawn token is also stored as
+    the row's next input and its position and length are advanced by one."""
     _need(logits, "logits", torch.float32, 2)
     rows, vocab = logits.shape
     if temperature is not None:
@@ -257,6 +266,8 @@ def sample(logits, temperature=None, request_key=None, position=None, status=Non
         out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
     rc = build.load("sampling").sb_sample(
         _ptr(logits), rows, vocab, ctypes.c_longlong(logits.stride(0)), _ptr(temperature),
-        _ptr(request_key), _ptr(position), _ptr(out), _ptr(status), _stream())
+        _ptr(request_key), _ptr(position), _ptr(out), _ptr(status),
+        _ptr(feed[0] if feed else None), _ptr(feed[1] if feed else None),
+        _ptr(feed[2] if feed else None), _stream())
     _check(rc, "sample")
     return out
