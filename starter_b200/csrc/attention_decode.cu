@@ -1,0 +1,248 @@
+// Single-token attention over the paged cache, split over the keys so that one long sequence fills
+// the GPU (engine/kernels/fused.py:729-823), with the query heads that share a key/value head handled
+// together so each key and value is read once (fused.py:641-709).
+//
+// Grid (row, kv_head * head_chunks, split).  A block walks the pages of its split; inside a page its
+// four warps take keys in turn, and inside a warp head_dim / 16 lanes share one key (16 elements each),
+// so a warp-wide load covers whole consecutive cache rows.  Every such lane group keeps its own running
+// maximum, sum and accumulator in float (fused.py:288-312); groups, warps and finally splits are merged
+// by rescaling onto the common maximum, and a part that saw no key drops out (fused.py:793-823).
+// Lengths come from device memory, so one captured launch serves every step (fused.py:262-271), and
+// they are per row.  A query at position p sees keys first..p, first = max(0, p + 1 - window).
+#include "common.cuh"
+
+#define AD_WARPS 4
+#define AD_MAXG 4
+#define AD_ELEMS 16
+
+template <typename T> __device__ __forceinline__ void load16(const T* p, float* out);
+template <> __device__ __forceinline__ void load16<bf16>(const bf16* p, float* out) {
+  const uint4 a = *reinterpret_cast<const uint4*>(p);
+  const uint4 b = *reinterpret_cast<const uint4*>(p + 8);
+  const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    out[2 * i] = __uint_as_float(w[i] << 16);
+    out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+template <> __device__ __forceinline__ void load16<float>(const float* p, float* out) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float4 v = *reinterpret_cast<const float4*>(p + 4 * i);
+    out[4 * i] = v.x; out[4 * i + 1] = v.y; out[4 * i + 2] = v.z; out[4 * i + 3] = v.w;
+  }
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(AD_WARPS * 32)
+attention_decode_kernel(const T* __restrict__ q, T* __restrict__ out, const T* __restrict__ k_store,
+                        const T* __restrict__ v_store, const int* __restrict__ block_table,
+                        int table_stride, const int* __restrict__ row_slot,
+                        const int* __restrict__ row_kv_len, int heads, int kv_heads, float scale_log2,
+                        int window, int n_splits, float* __restrict__ part_acc,
+                        float* __restrict__ part_ml) {
+  constexpr int LPK = D / AD_ELEMS;  // lanes that share a key
+  constexpr int KPW = 32 / LPK;      // keys a warp takes at a time
+  __shared__ float sh_acc[AD_WARPS][AD_MAXG][D];
+  __shared__ float sh_m[AD_WARPS][AD_MAXG];
+  __shared__ float sh_l[AD_WARPS][AD_MAXG];
+
+  const int groups = heads / kv_heads;
+  const int chunks = (groups + AD_MAXG - 1) / AD_MAXG;
+  const int row = blockIdx.x;
+  const int kvh = blockIdx.y / chunks;
+  const int g0 = (blockIdx.y % chunks) * AD_MAXG;
+  const int gc = min(AD_MAXG, groups - g0);
+  const int split = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int part = lane % LPK, sub = lane / LPK;
+
+  const int kv_len = row_kv_len[row];
+  int first = 0;
+  if (window > 0 && kv_len - window > 0) first = kv_len - window;
+  const int first_page = first / SB_PAGE_TOKENS;
+  const int end_page = (kv_len + SB_PAGE_TOKENS - 1) / SB_PAGE_TOKENS;
+  const int per_split = (end_page - first_page + n_splits - 1) / n_splits;
+  const int p_begin = first_page + split * per_split;
+  const int p_end = min(p_begin + per_split, end_page);
+  const int* pages = block_table + (size_t)row_slot[row] * table_stride;
+
+  float qv[AD_MAXG][AD_ELEMS], acc[AD_MAXG][AD_ELEMS], m[AD_MAXG], l[AD_MAXG];
+#pragma unroll
+  for (int g = 0; g < AD_MAXG; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+#pragma unroll
+    for (int i = 0; i < AD_ELEMS; ++i) acc[g][i] = 0.f;
+    if (g < gc) {
+      load16<T>(q + ((size_t)row * heads + (size_t)kvh * groups + g0 + g) * D + part * AD_ELEMS, qv[g]);
+#pragma unroll
+      for (int i = 0; i < AD_ELEMS; ++i) qv[g][i] *= scale_log2;
+    } else {
+#pragma unroll
+      for (int i = 0; i < AD_ELEMS; ++i) qv[g][i] = 0.f;
+    }
+  }
+
+  for (int p = p_begin; p < p_end; ++p) {
+    const size_t base = page_row(pages[p], kvh, 0, kv_heads, D);
+#pragma unroll 2
+    for (int k0 = warp * KPW; k0 < SB_PAGE_TOKENS; k0 += AD_WARPS * KPW) {
+      const int in_page = k0 + sub;
+      const int j = p * SB_PAGE_TOKENS + in_page;
+      const bool valid = j >= first && j < kv_len;
+      float kx[AD_ELEMS], vx[AD_ELEMS];
+      if (valid) {
+        load16<T>(k_store + base + (size_t)in_page * D + part * AD_ELEMS, kx);
+        load16<T>(v_store + base + (size_t)in_page * D + part * AD_ELEMS, vx);
+      } else {
+#pragma unroll
+        for (int i = 0; i < AD_ELEMS; ++i) kx[i] = vx[i] = 0.f;
+      }
+#pragma unroll
+      for (int g = 0; g < AD_MAXG; ++g) {
+        if (g < gc) {
+          float s = 0.f;
+#pragma unroll
+          for (int i = 0; i < AD_ELEMS; ++i) s += qv[g][i] * kx[i];
+#pragma unroll
+          for (int o = LPK / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+          if (valid) {
+            const float m_new = fmaxf(m[g], s);
+            const float alpha = exp2f(m[g] - m_new);
+            const float pr = exp2f(s - m_new);
+            l[g] = l[g] * alpha + pr;
+#pragma unroll
+            for (int i = 0; i < AD_ELEMS; ++i) acc[g][i] = acc[g][i] * alpha + pr * vx[i];
+            m[g] = m_new;
+          }
+        }
+      }
+    }
+  }
+
+  // merge the lane groups of a warp (same `part`, different `sub`)
+#pragma unroll
+  for (int g = 0; g < AD_MAXG; ++g) {
+    float m_all = m[g];
+#pragma unroll
+    for (int o = LPK; o < 32; o <<= 1) m_all = fmaxf(m_all, __shfl_xor_sync(0xffffffffu, m_all, o));
+    const float w = m[g] == -INFINITY ? 0.f : exp2f(m[g] - m_all);
+    float lsum = l[g] * w;
+#pragma unroll
+    for (int o = LPK; o < 32; o <<= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
+#pragma unroll
+    for (int i = 0; i < AD_ELEMS; ++i) {
+      float a = acc[g][i] * w;
+#pragma unroll
+      for (int o = LPK; o < 32; o <<= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+      acc[g][i] = a;
+    }
+    m[g] = m_all;
+    l[g] = lsum;
+    if (sub == 0) {
+#pragma unroll
+      for (int i = 0; i < AD_ELEMS; ++i) sh_acc[warp][g][part * AD_ELEMS + i] = acc[g][i];
+      if (part == 0) { sh_m[warp][g] = m_all; sh_l[warp][g] = lsum; }
+    }
+  }
+  __syncthreads();
+
+  // merge the warps; thread t finishes elements t, t + 128, ... of each head
+  for (int idx = threadIdx.x; idx < gc * D; idx += AD_WARPS * 32) {
+    const int g = idx / D, d = idx - g * D;
+    float m_all = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < AD_WARPS; ++w) m_all = fmaxf(m_all, sh_m[w][g]);
+    float lsum = 0.f, a = 0.f;
+#pragma unroll
+    for (int w = 0; w < AD_WARPS; ++w) {
+      const float wgt = sh_m[w][g] == -INFINITY ? 0.f : exp2f(sh_m[w][g] - m_all);
+      lsum += sh_l[w][g] * wgt;
+      a += sh_acc[w][g][d] * wgt;
+    }
+    const int head = kvh * groups + g0 + g;
+    if (n_splits == 1) {
+      out[((size_t)row * heads + head) * D + d] = from_f<T>(a / lsum);
+    } else {
+      const size_t slot = ((size_t)row * heads + head) * n_splits + split;
+      part_acc[slot * D + d] = a;
+      if (d == 0) { part_ml[slot * 2] = m_all; part_ml[slot * 2 + 1] = lsum; }
+    }
+  }
+}
+
+// out[row, head, :] = sum_s w_s acc_s / sum_s w_s l_s with w_s = 2^(m_s - max m)
+template <typename T>
+__global__ void attention_merge_kernel(const float* __restrict__ part_acc,
+                                       const float* __restrict__ part_ml, T* __restrict__ out,
+                                       int n_splits, int head_dim) {
+  const size_t rh = blockIdx.x;
+  float m_all = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) m_all = fmaxf(m_all, part_ml[(rh * n_splits + s) * 2]);
+  float lsum = 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float ms = part_ml[(rh * n_splits + s) * 2];
+    if (ms != -INFINITY) lsum += part_ml[(rh * n_splits + s) * 2 + 1] * exp2f(ms - m_all);
+  }
+  for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float ms = part_ml[(rh * n_splits + s) * 2];
+      if (ms != -INFINITY) a += part_acc[(rh * n_splits + s) * head_dim + d] * exp2f(ms - m_all);
+    }
+    out[rh * head_dim + d] = from_f<T>(a / lsum);
+  }
+}
+
+template <typename T, int D>
+static int launch(const void* q, void* out, const void* k_store, const void* v_store,
+                  const int* block_table, int table_stride, const int* row_slot, const int* row_kv_len,
+                  int rows, int heads, int kv_heads, float scale, int window, int n_splits,
+                  float* part_acc, float* part_ml, cudaStream_t s) {
+  const int groups = heads / kv_heads;
+  const int chunks = (groups + AD_MAXG - 1) / AD_MAXG;
+  dim3 grid(rows, kv_heads * chunks, n_splits);
+  attention_decode_kernel<T, D><<<grid, AD_WARPS * 32, 0, s>>>(
+      (const T*)q, (T*)out, (const T*)k_store, (const T*)v_store, block_table, table_stride, row_slot,
+      row_kv_len, heads, kv_heads, scale * 1.4426950408889634f, window, n_splits, part_acc, part_ml);
+  int rc = SB_LAUNCH_RESULT();
+  if (rc || n_splits == 1) return rc;
+  attention_merge_kernel<T><<<rows * heads, D < 128 ? D : 128, 0, s>>>(part_acc, part_ml, (T*)out,
+                                                                      n_splits, D);
+  return SB_LAUNCH_RESULT();
+}
+
+extern "C" {
+
+// q, out: [rows, heads * head_dim]; one query per row at position row_kv_len[row] - 1 of the sequence
+// in slot row_slot[row].  part_acc [rows * heads * n_splits * head_dim] and part_ml
+// [rows * heads * n_splits * 2] floats are scratch, unused when n_splits == 1.
+// head_dim must be 16, 32, 64, 128 or 256 (returns -2 otherwise).
+int sb_attention_decode(int dtype, const void* q, void* out, const void* k_store, const void* v_store,
+                        const int* block_table, int table_stride, const int* row_slot,
+                        const int* row_kv_len, int rows, int heads, int kv_heads, int head_dim,
+                        float scale, int window, int n_splits, float* part_acc, float* part_ml,
+                        cudaStream_t s) {
+  if (rows == 0) return 0;
+  if (kv_heads <= 0 || heads % kv_heads || n_splits < 1) return -2;
+#define ARGS q, out, k_store, v_store, block_table, table_stride, row_slot, row_kv_len, rows, heads, \
+             kv_heads, scale, window, n_splits, part_acc, part_ml, s
+#define BY_DTYPE(D)                                   \
+  if (dtype == 0) return launch<float, D>(ARGS);      \
+  if (dtype == 1) return launch<bf16, D>(ARGS);       \
+  return -1;
+  switch (head_dim) {
+    case 16: BY_DTYPE(16)
+    case 32: BY_DTYPE(32)
+    case 64: BY_DTYPE(64)
+    case 128: BY_DTYPE(128)
+    case 256: BY_DTYPE(256)
+    default: return -2;
+  }
+#undef BY_DTYPE
+#undef ARGS
+}
+
+}  // extern "C"

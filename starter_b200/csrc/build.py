@@ -34,6 +34,7 @@ SOURCES = (
     "elementwise",
     "rope_cache",
     "attention_rowwise",
+    "attention_decode",
     "linear_small",
     "sgemm",
     "sampling",

@@ -249,6 +249,51 @@ def attention_rowwise(q, k_store, v_store, block_table, tok_slot, tok_pos, heads
     return out
 
 
+DECODE_HEAD_DIMS = (16, 32, 64, 128, 256)
+
+
+def decode_splits(rows: int, kv_heads: int, groups: int) -> int:
+    """How many parts to cut each row's keys into so that about two blocks per SM are in flight."""
+    blocks = rows * kv_heads * ((groups + 3) // 4)
+    return max(1, min(32, -(-2 * 148 // blocks)))
+
+
+def attention_decode(q, k_store, v_store, block_table, row_slot, row_kv_len, heads, kv_heads, head_dim,
+                     scale, window=None, n_splits=None):
+    """One query per row (the newest token of its sequence) over that sequence's cached keys.
+
+    ``row_kv_len[r]`` is the sequence's length with the query's own key already filed; the lengths
+    stay on the device.  ``head_dim`` must be one of ``DECODE_HEAD_DIMS``."""
+    _need(q, "q", None, 2)
+    rows = q.shape[0]
+    if q.shape[1] != heads * head_dim:
+        raise KernelError(f"q has width {q.shape[1]}, expected {heads * head_dim}")
+    if head_dim not in DECODE_HEAD_DIMS:
+        raise KernelError(f"head_dim {head_dim} is not one of {DECODE_HEAD_DIMS}")
+    if heads % kv_heads:
+        raise KernelError(f"{heads} query heads cannot share {kv_heads} key/value heads")
+    for store in (k_store, v_store):
+        _need(store, "cache pages", q.dtype, 4)
+        if tuple(store.shape[1:]) != (kv_heads, PAGE_TOKENS, head_dim):
+            raise KernelError(f"cache pages have shape {tuple(store.shape)}")
+    _need(block_table, "block_table", torch.int32, 2)
+    _need(row_slot, "row_slot", torch.int32, 1)
+    _need(row_kv_len, "row_kv_len", torch.int32, 1)
+    if n_splits is None:
+        n_splits = decode_splits(rows, kv_heads, heads // kv_heads)
+    out = torch.empty_like(q)
+    part_acc = part_ml = None
+    if n_splits > 1:
+        part_acc = torch.empty((rows * heads * n_splits * head_dim,), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((rows * heads * n_splits * 2,), dtype=torch.float32, device=q.device)
+    rc = build.load("attention_decode").sb_attention_decode(
+        _code(q.dtype), _ptr(q), _ptr(out), _ptr(k_store), _ptr(v_store), _ptr(block_table),
+        block_table.shape[1], _ptr(row_slot), _ptr(row_kv_len), rows, heads, kv_heads, head_dim,
+        ctypes.c_float(scale), int(window or 0), n_splits, _ptr(part_acc), _ptr(part_ml), _stream())
+    _check(rc, "attention_decode")
+    return out
+
+
 # ---------------------------------------------------------------------------------------- sampling
 
 def sample(logits, temperature=None, request_key=None, position=None, status=None, out=None, feed=None):

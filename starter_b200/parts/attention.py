@@ -73,8 +73,12 @@ class GroupedQueryAttention(Part):
             qkv, s.num_heads, s.num_kv_heads, s.head_dim, self.q_norm, self.k_norm, s.qk_norm_eps,
             cos, sin, ctx.tok_pos, ctx.tok_slot, cache.block_table, keys, values,
             write_cache=writes_cache)
-        a = ops.attention_rowwise(q, keys, values, cache.block_table, ctx.tok_slot, ctx.tok_pos,
-                                  s.num_heads, s.num_kv_heads, s.head_dim, s.scale, s.window)
+        if ctx.max_q_len == 1 and s.head_dim in ops.DECODE_HEAD_DIMS:
+            a = ops.attention_decode(q, keys, values, cache.block_table, ctx.seq_slot, ctx.seq_kv_len,
+                                     s.num_heads, s.num_kv_heads, s.head_dim, s.scale, s.window)
+        else:
+            a = ops.attention_rowwise(q, keys, values, cache.block_table, ctx.tok_slot, ctx.tok_pos,
+                                      s.num_heads, s.num_kv_heads, s.head_dim, s.scale, s.window)
         return ops.linear(a, self.o)
 
     def weight_bytes(self):

@@ -245,3 +245,24 @@ def test_refusals_name_the_size():
         ops.linear(dev(torch.zeros(4, 8)).t(), dev(torch.zeros(3, 4)))
     with pytest.raises(ops.KernelError, match="width"):
         ops.linear(dev(torch.zeros(4, 8)), dev(torch.zeros(3, 9)))
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("heads,kv_heads,d,window,splits", [
+    (4, 2, 16, None, 1), (6, 2, 32, 5, 3), (8, 8, 128, None, 4), (8, 1, 64, 70, 2), (3, 1, 256, None, 7),
+    (32, 8, 128, None, None), (10, 2, 64, 64, 16)])
+def test_attention_decode_split_over_keys(dtype, heads, kv_heads, d, window, splits):
+    """One query per row; lengths 1 (a single key), 64 and 65 (a page's edge), 200; more splits than
+    pages (empty parts must drop out); a far key made to win; the window's first key."""
+    from starter_b200 import ops
+
+    lengths = [130, 1, 64, 65, 200]
+    c = attention_case(dtype, heads, kv_heads, d, lengths=lengths, new=[1] * 5, window=window, seed=40, spike=3)
+    kv_len = torch.tensor(lengths, dtype=torch.int32)
+    rows = torch.arange(5, dtype=torch.int32)
+    got = ops.attention_decode(dev(c["q"]), dev(c["ks"]), dev(c["vs"]), dev(c["table"]), dev(rows), dev(kv_len),
+                               heads, kv_heads, d, c["scale"], window, splits)
+    assert torch.allclose(got.cpu().float(), c["want"].float(), **TOL[dtype])
+    plain_kernel = ops.attention_rowwise(dev(c["q"]), dev(c["ks"]), dev(c["vs"]), dev(c["table"]), dev(c["slot"]),
+                                         dev(c["pos"]), heads, kv_heads, d, c["scale"], window)
+    assert torch.allclose(got.cpu().float(), plain_kernel.cpu().float(), **TOL[dtype])
