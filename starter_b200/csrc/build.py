@@ -37,6 +37,7 @@ SOURCES = (
     "attention_decode",
     "linear_small",
     "sgemm",
+    "gemm_tcgen05",
     "sampling",
 )
 

@@ -1,0 +1,399 @@
+// y[m, n] = sum_k x[m, k] * w[n, k] in bfloat16 on the fifth-generation tensor cores.
+//
+// The weight matrix is the streamed operand: a CTA owns 128 weight rows (the MMA's M) and up to 256
+// activation rows (the MMA's N), so the same kernel serves one decode row and a prompt.  TMA brings
+// [64 x 64] boxes of w and a [BM x 64] box of x into a ring of shared-memory stages (128-byte
+// swizzle, K-major); one thread issues tcgen05.mma (kind::f16, float accumulation in tensor memory);
+// four warps read the accumulator back with tcgen05.ld and write the result.  Rows past the end of
+// either matrix are zero-filled by TMA and masked on the way out, so no size needs padding.
+//
+// For a few rows the product is bound by reading w, and 128-row tiles alone would leave most SMs idle
+// (a 2560-row projection has 20), so the k range is cut into `splits` parts that run as separate CTAs.
+// Each writes its float partial tile to scratch; the last one to finish a tile (a counter per tile)
+// adds the parts in split order, so the sum does not depend on which CTA came last
+// (engine/kernels/fused.py:474-476), applies the epilogue and resets the counter.
+//
+// With `gated`, w is [gate; up] stacked ([2 * n_out, k]); a tile holds 64 gate rows and the matching
+// 64 up rows and the epilogue writes round(silu(gate)) * up (fused.py:89-112).
+//
+// Every wait on an mbarrier gives up after WAIT_LIMIT_NS, raises bit 4 of *status and lets the CTA
+// drain, free its tensor memory and return.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define TILE_N 128      // weight rows per CTA (MMA M)
+#define TILE_K 64       // k per stage: 128 bytes of bfloat16, one swizzle atom
+#define HALF_BYTES (64 * TILE_K * 2)
+#define A_BYTES (2 * HALF_BYTES)
+#define GEMM_THREADS 192
+#define GEMM_STAGES 4     // 74-98 KB of shared memory for bm <= 64: two or three CTAs share an SM
+#define WAIT_LIMIT_NS 2000000000ull
+
+// ------------------------------------------------------------------------------------------ PTX
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ uint64_t now_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+
+// Bounded wait: false (and *abort set) if the phase did not complete in time or another role gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
+  if (mbar_try(bar, parity)) return true;
+  const uint64_t start = now_ns();
+  while (true) {
+    if (mbar_try(bar, parity)) return true;
+    if (*abort) return false;
+    if (now_ns() - start > WAIT_LIMIT_NS) { *abort = 1; return false; }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* holder, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(holder)), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_free(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// The mbarrier gets one arrival when every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_load8(uint32_t taddr, float* v) {
+  uint32_t r[8];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// K-major operand tile, rows of 128 bytes, 128-byte swizzle: 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);   // start address
+  d |= (uint64_t)1 << 16;                    // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset
+  d |= (uint64_t)1 << 46;                    // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;                    // 128-byte swizzle
+  return d;
+}
+
+// kind::f16: float accumulator, bfloat16 A and B, both K-major, M = 128, N = bm.
+__device__ __forceinline__ uint32_t instr_desc(int bm) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bm >> 3) << 17) | ((uint32_t)(TILE_N >> 4) << 24);
+}
+
+// ------------------------------------------------------------------------------------------ kernel
+
+struct GemmArgs {
+  void* out;            // [rows, n_out] bfloat16 or float
+  float* scratch;       // [splits][tiles][TILE_N][bm] float partial tiles (splits > 1 or gated)
+  int* counters;        // one per (m tile, n tile), zero between launches
+  int* status;
+  int rows, n_out, k_dim;
+  int splits, gated, out_float;
+};
+
+template <int BM>
+__global__ void __launch_bounds__(GEMM_THREADS)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                    const GemmArgs args) {
+  constexpr int B_BYTES = BM * TILE_K * 2;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int STAGES = GEMM_STAGES;
+  constexpr uint32_t TMEM_COLS = BM < 32 ? 32 : BM;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
+  __shared__ uint32_t tmem_holder;
+  __shared__ int abort_flag, last_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x, split = blockIdx.y, mtile = blockIdx.z;
+  const int n_tiles = gridDim.x;
+  const int m0 = mtile * BM;
+  const int kb_total = (args.k_dim + TILE_K - 1) / TILE_K;
+  const int kb_per = (kb_total + args.splits - 1) / args.splits;
+  const int kb_begin = split * kb_per;
+  const int kb_end = min(kb_begin + kb_per, kb_total);
+  const int n_kb = max(kb_end - kb_begin, 0);
+  // rows of w in the two 64-row halves of the tile
+  const int row_a = args.gated ? tile * 64 : tile * TILE_N;
+  const int row_b = args.gated ? args.n_out + tile * 64 : tile * TILE_N + 64;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(&acc_bar, 1);
+    abort_flag = 0;
+    last_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(&tmem_holder, TMEM_COLS);
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = tmem_holder;
+  volatile int* abort = &abort_flag;
+
+  if (warp == 0) {
+    // ---------------- producer: one lane feeds the ring
+    if (lane == 0) {
+      int issued = 0;
+      for (int i = 0; i < n_kb; ++i) {
+        const int s = i % STAGES;
+        if (i >= STAGES && !mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, abort)) break;
+        uint8_t* a = smem + (size_t)s * STAGE_BYTES;
+        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+        const int k = (kb_begin + i) * TILE_K;
+        tma_load_2d(a, &map_w, &full_bar[s], k, row_a);
+        tma_load_2d(a + HALF_BYTES, &map_w, &full_bar[s], k, row_b);
+        tma_load_2d(a + A_BYTES, &map_x, &full_bar[s], k, m0);
+        issued = i + 1;
+      }
+      if (*abort) {
+        // copies still in flight write into this CTA's shared memory: give them time to land
+        for (int i = max(issued - STAGES, 0); i < issued; ++i) {
+          const uint64_t start = now_ns();
+          while (!mbar_try(&full_bar[i % STAGES], (i / STAGES) & 1) && now_ns() - start < WAIT_LIMIT_NS) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer: one lane
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc(BM);
+      bool ok = true;
+      for (int i = 0; i < n_kb && ok; ++i) {
+        const int s = i % STAGES;
+        ok = mbar_wait(&full_bar[s], (i / STAGES) & 1, abort);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
+        const uint64_t a_desc = smem_desc(a_addr), b_desc = smem_desc(a_addr + A_BYTES);
+#pragma unroll
+        for (int k = 0; k < TILE_K / 16; ++k) {
+          // 16 elements of k are 32 bytes: 2 units of the descriptor's 16-byte address
+          umma_bf16(tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty_bar[s]);
+      }
+      umma_commit(&acc_bar);
+    }
+  } else {
+    // ---------------- epilogue: warps 2..5 own the TMEM lane quarters 2, 3, 0, 1
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;                 // row of the tile = TMEM lane
+    const bool have = n_kb > 0 && mbar_wait(&acc_bar, 0, abort);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int rows_here = min(BM, args.rows - m0);
+    const bool direct = args.splits == 1 && !args.gated;
+    const int n = tile * TILE_N + r;                   // output column when not gated
+    float* part = args.scratch + (((size_t)(mtile * gridDim.y + split) * n_tiles + tile) * TILE_N + r) * BM;
+    if (have || n_kb == 0) {
+#pragma unroll 1
+      for (int c = 0; c < BM; c += 8) {
+        float v[8];
+        if (have) tmem_load8(tmem + ((uint32_t)(quarter * 32) << 16) + c, v);
+        else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = 0.f;
+        }
+        if (direct) {
+          if (n < args.n_out) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int m = c + j;
+              if (m < rows_here) {
+                const size_t at = (size_t)(m0 + m) * args.n_out + n;
+                if (args.out_float) ((float*)args.out)[at] = v[j];
+                else ((bf16*)args.out)[at] = __float2bfloat16_rn(v[j]);
+              }
+            }
+          }
+        } else {
+          *reinterpret_cast<float4*>(part + c) = make_float4(v[0], v[1], v[2], v[3]);
+          *reinterpret_cast<float4*>(part + c + 4) = make_float4(v[4], v[5], v[6], v[7]);
+        }
+      }
+    }
+    if (!direct) {
+      // publish the partial tile, then the last CTA of this tile adds the parts in split order
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 64) {
+        const int ticket = atomicAdd(&args.counters[mtile * n_tiles + tile], 1);
+        last_flag = ticket == args.splits - 1;
+        if (last_flag) args.counters[mtile * n_tiles + tile] = 0;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (last_flag && !*abort) {
+        __threadfence();
+        const int t = threadIdx.x - 64;                // 0..127
+        const float* base = args.scratch + ((size_t)(mtile * gridDim.y) * n_tiles + tile) * TILE_N * BM;
+        const size_t split_stride = (size_t)n_tiles * TILE_N * BM;
+        const int out_rows = args.gated ? 64 : TILE_N;
+        // thread t takes output row (t % out_rows) and every (128 / out_rows)-th activation row
+        const int orow = t % out_rows;
+        const int ncol = (args.gated ? tile * 64 : tile * TILE_N) + orow;
+        for (int m = t / out_rows; m < rows_here; m += 128 / out_rows) {
+          float g = 0.f, u = 0.f;
+          for (int s = 0; s < args.splits; ++s) {
+            const float* p = base + s * split_stride;
+            g += __ldcg(p + (size_t)orow * BM + m);
+            if (args.gated) u += __ldcg(p + (size_t)(orow + 64) * BM + m);
+          }
+          if (ncol < args.n_out) {
+            float y = g;
+            if (args.gated) {
+              const float gr = rnd<bf16>(g), ur = rnd<bf16>(u);
+              y = rnd<bf16>(gr / (1.f + __expf(-gr))) * ur;
+            }
+            const size_t at = (size_t)(m0 + m) * args.n_out + ncol;
+            if (args.out_float) ((float*)args.out)[at] = y;
+            else ((bf16*)args.out)[at] = __float2bfloat16_rn(y);
+          }
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) tmem_free(tmem, TMEM_COLS);
+  if (threadIdx.x == 0 && abort_flag && args.status) atomicOr(args.status, 4);
+}
+
+// ------------------------------------------------------------------------------------------ host
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// A [rows, k] row-major bfloat16 matrix read in boxes of [box_rows x 64] with 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, int rows, int k_dim, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return -3;
+  cuuint64_t dims[2] = {(cuuint64_t)k_dim, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)k_dim * 2};
+  cuuint32_t box[2] = {TILE_K, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims, strides, box, elem,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS ? 0 : -4;
+}
+
+template <int BM>
+static int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const GemmArgs& args, int tiles,
+                  int m_tiles, cudaStream_t s) {
+  constexpr int STAGE_BYTES = A_BYTES + BM * TILE_K * 2;
+  constexpr int STAGES = GEMM_STAGES;
+  const int smem = STAGES * STAGE_BYTES + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BM>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid(tiles, args.splits, m_tiles);
+  gemm_tcgen05_kernel<BM><<<grid, GEMM_THREADS, smem, s>>>(map_w, map_x, args);
+  return SB_LAUNCH_RESULT();
+}
+
+extern "C" {
+
+// Bytes of float scratch the call needs (0 when the result is written straight from tensor memory).
+long long sb_gemm_tcgen05_scratch(int rows, int n_out, int splits, int gated, int bm) {
+  if (splits == 1 && !gated) return 0;
+  const long long tiles = gated ? (n_out + 63) / 64 : (n_out + TILE_N - 1) / TILE_N;
+  const long long m_tiles = (rows + bm - 1) / bm;
+  return m_tiles * splits * tiles * TILE_N * bm * 4;
+}
+
+// x [rows, k_dim] and w [n_out (2 * n_out if gated), k_dim] bfloat16, row-major, 16-byte aligned,
+// k_dim a multiple of 8.  bm (16, 32, 64, 128 or 256) is the number of activation rows per tile.
+// counters: at least ceil(rows / bm) * tiles ints, zero on entry and zero again on exit.
+// Returns -2 for sizes it does not take, -3/-4 if the tensor maps cannot be made.
+int sb_gemm_tcgen05(const void* x, const void* w, void* out, int rows, int n_out, int k_dim, int bm,
+                    int splits, int gated, int out_float, float* scratch, int* counters, int* status,
+                    cudaStream_t s) {
+  if (rows == 0 || n_out == 0) return 0;
+  if (k_dim % 8 || k_dim <= 0 || splits < 1) return -2;
+  if (((uintptr_t)x | (uintptr_t)w) & 15) return -2;
+  if (gated && n_out % 64) return -2;
+  const int tiles = gated ? n_out / 64 : (n_out + TILE_N - 1) / TILE_N;
+  const int m_tiles = (rows + bm - 1) / bm;
+  const int w_rows = gated ? 2 * n_out : n_out;
+  CUtensorMap map_w, map_x;
+  int rc = make_map(&map_w, w, w_rows, k_dim, 64);
+  if (rc) return rc;
+  rc = make_map(&map_x, x, rows, k_dim, bm);
+  if (rc) return rc;
+  GemmArgs args;
+  args.out = out; args.scratch = scratch; args.counters = counters; args.status = status;
+  args.rows = rows; args.n_out = n_out; args.k_dim = k_dim;
+  args.splits = splits; args.gated = gated; args.out_float = out_float;
+  switch (bm) {
+    case 16: return launch<16>(map_w, map_x, args, tiles, m_tiles, s);
+    case 32: return launch<32>(map_w, map_x, args, tiles, m_tiles, s);
+    case 64: return launch<64>(map_w, map_x, args, tiles, m_tiles, s);
+    case 128: return launch<128>(map_w, map_x, args, tiles, m_tiles, s);
+    case 256: return launch<256>(map_w, map_x, args, tiles, m_tiles, s);
+    default: return -2;
+  }
+}
+
+}  // extern "C"

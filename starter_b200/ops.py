@@ -149,6 +149,8 @@ def linear(x, weight, out_float=False, gated=False):
         raise KernelError(f"a gated weight needs an even number of rows, got {n_total}")
     n_out = n_total // 2 if gated else n_total
     dt = _code(x.dtype)
+    if dt == 1 and tensor_core_ok(x, weight, gated, n_out):
+        return linear_tensor_core(x, weight, out_float=out_float, gated=gated)
     if rows <= SMALL_ROWS:
         out_dtype = torch.float32 if (out_float or dt == 0) else x.dtype
         if gated and out_float and dt == 1:
@@ -169,6 +171,71 @@ def linear(x, weight, out_float=False, gated=False):
     else:
         y = torch.mm(x, weight.t())
     return swiglu(y) if gated else y
+
+
+GEMM_MAX_TILES = 1 << 16
+_gemm_counters = {}
+
+
+def tensor_core_ok(x, weight, gated, n_out) -> bool:
+    """Whether the tcgen05 product takes these operands: k a multiple of 8 (16-byte rows for TMA),
+    16-byte aligned bases, gated widths in steps of 64."""
+    k_dim = x.shape[1]
+    if k_dim % 8 or x.data_ptr() % 16 or weight.data_ptr() % 16:
+        return False
+    if gated and n_out % 64:
+        return False
+    return True
+
+
+def gemm_plan(rows: int, n_out: int, k_dim: int, gated: bool):
+    """``(bm, splits)``: activation rows per tile, and into how many CTAs the k range is cut so that
+    about two CTAs per SM stream the weights."""
+    bm = 16
+    while bm < rows and bm < 256:
+        bm *= 2
+    tiles = (n_out // 64 if gated else -(-n_out // 128)) * -(-rows // bm)
+    k_blocks = -(-k_dim // 64)
+    splits = max(1, min(k_blocks // 4, round(2 * 148 / tiles)))
+    if rows > 64:
+        splits = 1 if tiles >= 100 else max(1, min(k_blocks // 8, 148 // tiles))
+    return bm, splits
+
+
+def linear_tensor_core(x, weight, out_float=False, gated=False, bm=None, splits=None, status=None):
+    """The bfloat16 product on tcgen05 tensor cores (csrc/gemm_tcgen05.cu)."""
+    _need(x, "x", torch.bfloat16, 2)
+    _need(weight, "weight", torch.bfloat16, 2)
+    rows, k_dim = x.shape
+    n_total = weight.shape[0]
+    n_out = n_total // 2 if gated else n_total
+    if weight.shape[1] != k_dim:
+        raise KernelError(f"weight {tuple(weight.shape)} does not take inputs of width {k_dim}")
+    if not tensor_core_ok(x, weight, gated, n_out):
+        raise KernelError(f"the tensor-core product needs k % 8 == 0, 16-byte aligned operands and gated "
+                          f"widths in steps of 64; got k = {k_dim}, n = {n_out}")
+    plan_bm, plan_splits = gemm_plan(rows, n_out, k_dim, gated)
+    bm = bm or plan_bm
+    splits = splits or plan_splits
+    lib = build.load("gemm_tcgen05")
+    lib.sb_gemm_tcgen05_scratch.restype = ctypes.c_longlong
+    tiles = (n_out // 64 if gated else -(-n_out // 128)) * -(-rows // bm)
+    if tiles > GEMM_MAX_TILES:
+        raise KernelError(f"{tiles} output tiles exceed the {GEMM_MAX_TILES} the counters cover")
+    dev = x.device
+    if dev not in _gemm_counters:
+        _gemm_counters[dev] = torch.zeros((GEMM_MAX_TILES,), dtype=torch.int32, device=dev)
+    need = lib.sb_gemm_tcgen05_scratch(rows, n_out, splits, int(gated), bm)
+    scratch = torch.empty((need // 4,), dtype=torch.float32, device=dev) if need else None
+    out = torch.empty((rows, n_out), dtype=torch.float32 if out_float else torch.bfloat16, device=dev)
+    rc = lib.sb_gemm_tcgen05(_ptr(x), _ptr(weight), _ptr(out), rows, n_out, k_dim, bm, splits, int(gated),
+                             int(out_float), _ptr(scratch), _ptr(_gemm_counters[dev]), _ptr(status),
+                             _stream())
+    if rc in (-3, -4):
+        raise KernelError("the TMA descriptors for the tensor-core product could not be made "
+                          f"(code {rc}); is the driver too old for cuTensorMapEncodeTiled?")
+    _check(rc, "gemm_tcgen05")
+    return out
 
 
 # ---------------------------------------------------------------------------------------- attention

@@ -266,3 +266,32 @@ def test_attention_decode_split_over_keys(dtype, heads, kv_heads, d, window, spl
     plain_kernel = ops.attention_rowwise(dev(c["q"]), dev(c["ks"]), dev(c["vs"]), dev(c["table"]), dev(c["slot"]),
                                          dev(c["pos"]), heads, kv_heads, d, c["scale"], window)
     assert torch.allclose(got.cpu().float(), plain_kernel.cpu().float(), **TOL[dtype])
+
+
+@pytest.mark.parametrize("rows,n,k,gated,bm,splits", [
+    (1, 128, 64, False, 16, 1), (8, 256, 512, False, 16, 2), (5, 300, 1000, False, None, None),
+    (16, 2560, 4096, False, None, None), (64, 1000, 2560, False, None, None), (3, 200, 264, False, 16, 9),
+    (8, 1216, 2560, True, None, None), (33, 640, 2568, True, None, 3), (1, 64, 8, True, 16, 1),
+    (200, 520, 1000, False, None, None), (600, 777, 264, False, 256, 1), (257, 130, 72, False, 128, 2)])
+def test_tensor_core_product(rows, n, k, gated, bm, splits):
+    """The tcgen05 product at sizes that are no multiples of its tiles, with and without splitting k,
+    plain and gated, bfloat16 and float32 results; and twice, since it keeps counters between calls."""
+    from starter_b200 import ops
+
+    x = rand(rows, k, dtype="bfloat16", seed=50)
+    w = rand(n * (2 if gated else 1), k, dtype="bfloat16", seed=51, scale=0.05)
+    ref = x.double() @ w.double().t()
+    if gated:
+        gu = ref.to(torch.bfloat16)
+        ref = plain.plain_swiglu(gu[:, :n], gu[:, n:]).double()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for _ in range(2):
+        got = ops.linear_tensor_core(dev(x), dev(w), gated=gated, bm=bm, splits=splits, status=status)
+        assert got.shape == (rows, n) and got.dtype == torch.bfloat16
+        assert torch.allclose(got.cpu().double(), ref, atol=2e-2, rtol=2e-2)
+    if not gated:
+        got32 = ops.linear_tensor_core(dev(x), dev(w), out_float=True, bm=bm, splits=splits, status=status)
+        assert torch.allclose(got32.cpu().double(), ref, atol=1e-4, rtol=1e-4)
+        again = ops.linear_tensor_core(dev(x), dev(w), out_float=True, bm=bm, splits=splits, status=status)
+        assert torch.equal(got32, again)            # parts are added in split order, whoever ends last
+    assert status.item() == 0
