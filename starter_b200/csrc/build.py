@@ -35,6 +35,7 @@ SOURCES = (
     "rope_cache",
     "attention_rowwise",
     "attention_decode",
+    "attention_prefill",
     "linear_small",
     "sgemm",
     "gemm_tcgen05",

@@ -272,25 +272,46 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const float* base = args.scratch + ((size_t)(mtile * gridDim.y) * n_tiles + tile) * TILE_N * BM;
         const size_t split_stride = (size_t)n_tiles * TILE_N * BM;
         const int out_rows = args.gated ? 64 : TILE_N;
-        // thread t takes output row (t % out_rows) and every (128 / out_rows)-th activation row
-        const int orow = t % out_rows;
-        const int ncol = (args.gated ? tile * 64 : tile * TILE_N) + orow;
-        for (int m = t / out_rows; m < rows_here; m += 128 / out_rows) {
-          float g = 0.f, u = 0.f;
-          for (int s = 0; s < args.splits; ++s) {
-            const float* p = base + s * split_stride;
-            g += __ldcg(p + (size_t)orow * BM + m);
-            if (args.gated) u += __ldcg(p + (size_t)(orow + 64) * BM + m);
+        // an item is one output column and four activation rows; the loads of up to eight parts
+        // are in flight together and are added in split order
+        const int quads = (rows_here + 3) / 4;
+        for (int item = t; item < out_rows * quads; item += 128) {
+          const int orow = item % out_rows, m = (item / out_rows) * 4;
+          const int ncol = (args.gated ? tile * 64 : tile * TILE_N) + orow;
+          float4 g = make_float4(0.f, 0.f, 0.f, 0.f), u = g;
+          for (int s0 = 0; s0 < args.splits; s0 += 8) {
+            float4 gv[8], uv[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if (s0 + j < args.splits) {
+                const float* p = base + (size_t)(s0 + j) * split_stride + (size_t)orow * BM + m;
+                gv[j] = __ldcg(reinterpret_cast<const float4*>(p));
+                if (args.gated) uv[j] = __ldcg(reinterpret_cast<const float4*>(p + 64 * BM));
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if (s0 + j < args.splits) {
+                g.x += gv[j].x; g.y += gv[j].y; g.z += gv[j].z; g.w += gv[j].w;
+                if (args.gated) { u.x += uv[j].x; u.y += uv[j].y; u.z += uv[j].z; u.w += uv[j].w; }
+              }
+            }
           }
           if (ncol < args.n_out) {
-            float y = g;
-            if (args.gated) {
-              const float gr = rnd<bf16>(g), ur = rnd<bf16>(u);
-              y = rnd<bf16>(gr / (1.f + __expf(-gr))) * ur;
+            const float gs[4] = {g.x, g.y, g.z, g.w}, us[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (m + j < rows_here) {
+                float y = gs[j];
+                if (args.gated) {
+                  const float gr = rnd<bf16>(gs[j]), ur = rnd<bf16>(us[j]);
+                  y = rnd<bf16>(gr / (1.f + __expf(-gr))) * ur;
+                }
+                const size_t at = (size_t)(m0 + m + j) * args.n_out + ncol;
+                if (args.out_float) ((float*)args.out)[at] = y;
+                else ((bf16*)args.out)[at] = __float2bfloat16_rn(y);
+              }
             }
-            const size_t at = (size_t)(m0 + m) * args.n_out + ncol;
-            if (args.out_float) ((float*)args.out)[at] = y;
-            else ((bf16*)args.out)[at] = __float2bfloat16_rn(y);
           }
         }
       }

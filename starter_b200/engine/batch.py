@@ -16,6 +16,9 @@ import numpy as np
 import torch
 
 
+QUERY_TILE = 64
+
+
 @dataclass
 class StepEntry:
     """One sequence's share of a step: its slot, its next tokens, and the places (indices into
@@ -38,6 +41,8 @@ class StepContext:
     seq_q_len: torch.Tensor
     seq_kv_len: torch.Tensor
     want_rows: torch.Tensor
+    tile_seq: torch.Tensor      # work list of the many-token attention: per tile of 64 queries its
+    tile_first: torch.Tensor    # sequence (index into the seq_* arrays) and its first query there
     max_q_len: int
     max_kv_len: int
     cache: object
@@ -80,9 +85,14 @@ def plan_step(entries, starts, vocab_size=None):
         q_start.append(base)
         q_len.append(n)
         kv_len.append(start + n)
+    # tiles of 64 queries, the ones with most keys to walk first
+    tiles = [(kv_len[i] - q_len[i] + first, i, first)
+             for i in range(len(entries)) for first in range(0, q_len[i], QUERY_TILE)]
+    tiles.sort(key=lambda t: -t[0])
     arrays = {
         "tokens": tokens, "tok_pos": tok_pos, "tok_slot": tok_slot, "seq_slot": slots,
         "seq_q_start": q_start, "seq_q_len": q_len, "seq_kv_len": kv_len, "want_rows": want_rows,
+        "tile_seq": [t[1] for t in tiles], "tile_first": [t[2] for t in tiles],
     }
     return {k: np.asarray(v, dtype=np.int32) for k, v in arrays.items()}
 

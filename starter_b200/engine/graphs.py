@@ -33,6 +33,7 @@ class DecodeGraphs:
         self.meta = torch.zeros((len(self.fields), max_batch), dtype=torch.int32, device=dev)
         self.rows = torch.arange(max_batch, dtype=torch.int32, device=dev)
         self.ones = torch.ones(max_batch, dtype=torch.int32, device=dev)
+        self.zeros = torch.zeros(max_batch, dtype=torch.int32, device=dev)
         self.out = torch.zeros(max_batch, dtype=torch.int32, device=dev)
         self.graphs = {}
         self.logits = {}
@@ -49,6 +50,7 @@ class DecodeGraphs:
             tok_slot=self._field("tok_slot", batch), seq_slot=self._field("tok_slot", batch),
             seq_q_start=self.rows[:batch], seq_q_len=self.ones[:batch],
             seq_kv_len=self._field("kv_len", batch), want_rows=self.rows[:batch],
+            tile_seq=self.rows[:batch], tile_first=self.zeros[:batch],
             max_q_len=1, max_kv_len=0, cache=self.runner.cache, status=self.runner.status, host=None)
 
     def _body(self, batch: int):

@@ -127,6 +127,7 @@ class ModelRunner:
             tokens=dev["tokens"], tok_pos=dev["tok_pos"], tok_slot=dev["tok_slot"],
             seq_slot=dev["seq_slot"], seq_q_start=dev["seq_q_start"], seq_q_len=dev["seq_q_len"],
             seq_kv_len=dev["seq_kv_len"], want_rows=dev["want_rows"],
+            tile_seq=dev["tile_seq"], tile_first=dev["tile_first"],
             max_q_len=int(arrays["seq_q_len"].max()), max_kv_len=max_kv,
             cache=cache, status=self.status, host=arrays)
 
@@ -179,4 +180,8 @@ class ModelRunner:
                 problems.append("a token id outside the vocabulary reached the embedding")
             if code & 2:
                 problems.append("a row of logits held no finite value")
+            if code & 4:
+                problems.append("a wait inside the tensor-core product ran out of time")
+            if code & 8:
+                problems.append("a wait inside the decode attention kernel ran out of time")
             raise RuntimeError("; ".join(problems) or f"device status {code}")

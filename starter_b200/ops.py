@@ -316,17 +316,58 @@ def attention_rowwise(q, k_store, v_store, block_table, tok_slot, tok_pos, heads
     return out
 
 
+PREFILL_HEAD_DIMS = (16, 32, 64, 128)
+
+
+def attention_prefill(q, k_store, v_store, block_table, seq_slot, seq_q_start, seq_q_len, seq_kv_len,
+                      tile_seq, tile_first, heads, kv_heads, head_dim, scale, window=None):
+    """Causal attention for steps with many tokens per sequence (bfloat16, tensor cores).
+
+    ``q`` ``[T, heads * head_dim]`` packed by sequence; the ``seq_*`` arrays describe each sequence
+    of the step, ``tile_seq``/``tile_first`` list the tiles of 64 queries."""
+    _need(q, "q", torch.bfloat16, 2)
+    if q.shape[1] != heads * head_dim:
+        raise KernelError(f"q has width {q.shape[1]}, expected {heads * head_dim}")
+    if head_dim not in PREFILL_HEAD_DIMS:
+        raise KernelError(f"head_dim {head_dim} is not one of {PREFILL_HEAD_DIMS}")
+    if heads % kv_heads:
+        raise KernelError(f"{heads} query heads cannot share {kv_heads} key/value heads")
+    for store in (k_store, v_store):
+        _need(store, "cache pages", q.dtype, 4)
+        if tuple(store.shape[1:]) != (kv_heads, PAGE_TOKENS, head_dim):
+            raise KernelError(f"cache pages have shape {tuple(store.shape)}")
+    _need(block_table, "block_table", torch.int32, 2)
+    for name, t in (("seq_slot", seq_slot), ("seq_q_start", seq_q_start), ("seq_q_len", seq_q_len),
+                    ("seq_kv_len", seq_kv_len), ("tile_seq", tile_seq), ("tile_first", tile_first)):
+        _need(t, name, torch.int32, 1)
+    out = torch.empty_like(q)
+    rc = build.load("attention_prefill").sb_attention_prefill(
+        _ptr(q), _ptr(out), _ptr(k_store), _ptr(v_store), _ptr(block_table), block_table.shape[1],
+        _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), _ptr(seq_kv_len), _ptr(tile_seq),
+        _ptr(tile_first), tile_seq.shape[0], heads, kv_heads, head_dim, ctypes.c_float(scale),
+        int(window or 0), _stream())
+    _check(rc, "attention_prefill")
+    return out
+
+
 DECODE_HEAD_DIMS = (16, 32, 64, 128, 256)
 
 
+def decode_attention_takes(head_dim: int, dtype) -> bool:
+    """Whether the split-key decode kernel takes this head size: 16 elements per lane, and two
+    stages of a page's keys and values (2 * 2 * 64 * head_dim elements) within shared memory."""
+    return head_dim in DECODE_HEAD_DIMS and head_dim * dtype.itemsize <= 512
+
+
 def decode_splits(rows: int, kv_heads: int, groups: int) -> int:
-    """How many parts to cut each row's keys into so that about two blocks per SM are in flight."""
+    """How many parts to cut each row's keys into: as many as keep all blocks resident at once
+    (two per SM), so that no block waits for a second wave."""
     blocks = rows * kv_heads * ((groups + 3) // 4)
-    return max(1, min(32, -(-2 * 148 // blocks)))
+    return max(1, min(32, (2 * 148) // blocks))
 
 
 def attention_decode(q, k_store, v_store, block_table, row_slot, row_kv_len, heads, kv_heads, head_dim,
-                     scale, window=None, n_splits=None):
+                     scale, window=None, n_splits=None, status=None):
     """One query per row (the newest token of its sequence) over that sequence's cached keys.
 
     ``row_kv_len[r]`` is the sequence's length with the query's own key already filed; the lengths
@@ -335,8 +376,9 @@ def attention_decode(q, k_store, v_store, block_table, row_slot, row_kv_len, hea
     rows = q.shape[0]
     if q.shape[1] != heads * head_dim:
         raise KernelError(f"q has width {q.shape[1]}, expected {heads * head_dim}")
-    if head_dim not in DECODE_HEAD_DIMS:
-        raise KernelError(f"head_dim {head_dim} is not one of {DECODE_HEAD_DIMS}")
+    if not decode_attention_takes(head_dim, q.dtype):
+        raise KernelError(f"head_dim {head_dim} in {q.dtype} is outside what the decode kernel takes: "
+                          f"one of {DECODE_HEAD_DIMS} and at most 512 bytes per head row")
     if heads % kv_heads:
         raise KernelError(f"{heads} query heads cannot share {kv_heads} key/value heads")
     for store in (k_store, v_store):
@@ -356,7 +398,8 @@ def attention_decode(q, k_store, v_store, block_table, row_slot, row_kv_len, hea
     rc = build.load("attention_decode").sb_attention_decode(
         _code(q.dtype), _ptr(q), _ptr(out), _ptr(k_store), _ptr(v_store), _ptr(block_table),
         block_table.shape[1], _ptr(row_slot), _ptr(row_kv_len), rows, heads, kv_heads, head_dim,
-        ctypes.c_float(scale), int(window or 0), n_splits, _ptr(part_acc), _ptr(part_ml), _stream())
+        ctypes.c_float(scale), int(window or 0), n_splits, _ptr(part_acc), _ptr(part_ml),
+        _ptr(status), _stream())
     _check(rc, "attention_decode")
     return out
 
@@ -376,10 +419,14 @@ def sample(logits, temperature=None, request_key=None, position=None, status=Non
         _need(position, "position", torch.int32, 1)
     if out is None:
         out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
-    rc = build.load("sampling").sb_sample(
+    lib = build.load("sampling")
+    chunks = lib.sb_sample_chunks(vocab)
+    cand_v = torch.empty((rows * chunks,), dtype=torch.float32, device=logits.device)
+    cand_i = torch.empty((rows * chunks,), dtype=torch.int32, device=logits.device)
+    rc = lib.sb_sample(
         _ptr(logits), rows, vocab, ctypes.c_longlong(logits.stride(0)), _ptr(temperature),
         _ptr(request_key), _ptr(position), _ptr(out), _ptr(status),
         _ptr(feed[0] if feed else None), _ptr(feed[1] if feed else None),
-        _ptr(feed[2] if feed else None), _stream())
+        _ptr(feed[2] if feed else None), _ptr(cand_v), _ptr(cand_i), _stream())
     _check(rc, "sample")
     return out

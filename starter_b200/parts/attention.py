@@ -73,9 +73,14 @@ class GroupedQueryAttention(Part):
             qkv, s.num_heads, s.num_kv_heads, s.head_dim, self.q_norm, self.k_norm, s.qk_norm_eps,
             cos, sin, ctx.tok_pos, ctx.tok_slot, cache.block_table, keys, values,
             write_cache=writes_cache)
-        if ctx.max_q_len == 1 and s.head_dim in ops.DECODE_HEAD_DIMS:
+        if ctx.max_q_len == 1 and ops.decode_attention_takes(s.head_dim, q.dtype):
             a = ops.attention_decode(q, keys, values, cache.block_table, ctx.seq_slot, ctx.seq_kv_len,
-                                     s.num_heads, s.num_kv_heads, s.head_dim, s.scale, s.window)
+                                     s.num_heads, s.num_kv_heads, s.head_dim, s.scale, s.window,
+                                     status=ctx.status)
+        elif q.dtype == torch.bfloat16 and s.head_dim in ops.PREFILL_HEAD_DIMS:
+            a = ops.attention_prefill(q, keys, values, cache.block_table, ctx.seq_slot, ctx.seq_q_start,
+                                      ctx.seq_q_len, ctx.seq_kv_len, ctx.tile_seq, ctx.tile_first,
+                                      s.num_heads, s.num_kv_heads, s.head_dim, s.scale, s.window)
         else:
             a = ops.attention_rowwise(q, keys, values, cache.block_table, ctx.tok_slot, ctx.tok_pos,
                                       s.num_heads, s.num_kv_heads, s.head_dim, s.scale, s.window)

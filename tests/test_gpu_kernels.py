@@ -256,6 +256,11 @@ def test_attention_decode_split_over_keys(dtype, heads, kv_heads, d, window, spl
     pages (empty parts must drop out); a far key made to win; the window's first key."""
     from starter_b200 import ops
 
+    if not ops.decode_attention_takes(d, DT[dtype]):
+        with pytest.raises(ops.KernelError, match="head_dim"):
+            ops.attention_decode(dev(torch.zeros(1, heads * d, dtype=DT[dtype])), None, None, None, None, None,
+                                 heads, kv_heads, d, 1.0)
+        return
     lengths = [130, 1, 64, 65, 200]
     c = attention_case(dtype, heads, kv_heads, d, lengths=lengths, new=[1] * 5, window=window, seed=40, spike=3)
     kv_len = torch.tensor(lengths, dtype=torch.int32)
@@ -295,3 +300,21 @@ def test_tensor_core_product(rows, n, k, gated, bm, splits):
         again = ops.linear_tensor_core(dev(x), dev(w), out_float=True, bm=bm, splits=splits, status=status)
         assert torch.equal(got32, again)            # parts are added in split order, whoever ends last
     assert status.item() == 0
+
+
+@pytest.mark.parametrize("heads,kv_heads,d,window", [(4, 2, 16, None), (6, 2, 32, 5), (8, 8, 128, None),
+                                                    (8, 1, 64, 70), (32, 8, 128, None), (4, 4, 64, 64)])
+def test_attention_prefill_many_tokens_per_sequence(heads, kv_heads, d, window):
+    """Whole prompts, a chunk that continues a sequence (its first query is not at position 0), one
+    query, lengths at and next to the tile and page edges, scattered pages, a far key made to win."""
+    from starter_b200 import ops
+
+    lengths, new = [130, 1, 64, 200, 65, 300], [130, 1, 3, 77, 65, 129]
+    c = attention_case("bfloat16", heads, kv_heads, d, lengths=lengths, new=new, window=window, seed=60, spike=2)
+    q_start = [sum(new[:i]) for i in range(len(new))]
+    tiles = [(i, f) for i in range(len(new)) for f in range(0, new[i], 64)]
+    ints = lambda v: dev(torch.tensor(v, dtype=torch.int32))
+    got = ops.attention_prefill(dev(c["q"]), dev(c["ks"]), dev(c["vs"]), dev(c["table"]), ints(list(range(len(new)))),
+                                ints(q_start), ints(new), ints(lengths), ints([t[0] for t in tiles]),
+                                ints([t[1] for t in tiles]), heads, kv_heads, d, c["scale"], window)
+    assert torch.allclose(got.cpu().float(), c["want"].float(), atol=2e-2, rtol=2e-2)
