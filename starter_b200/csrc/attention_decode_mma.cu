@@ -1,0 +1,313 @@
+// Single-token attention over the paged cache on tensor cores (bfloat16), split over the keys.
+//
+// The CUDA-core decode kernel (attention_decode.cu) spends about a hundred instructions per key and
+// head group, which at large batch costs more time than reading the keys.  Here the query heads that
+// share a key/value head (engine/kernels/fused.py:641-709) form the 16 rows of an mma.sync tile
+// (rows past the group are zero), the keys are its columns, and a key costs a handful of
+// instructions.  Grid (row, kv_head * head_chunks, split) as in the CUDA-core kernel, and the same
+// scratch and merge kernel for the splits (fused.py:729-823).
+//
+// A CTA walks the pages of its split.  All four warps copy a page (keys and values, 64 x head_dim
+// each) into a ring of shared-memory stages with 16-byte asynchronous copies, three pages ahead,
+// XOR-swizzled for ldmatrix; each warp then takes 16 of the page's 64 keys: S = Q K^T (16 x 16),
+// online softmax in float (fused.py:288-312), P rounded to bfloat16 (fused.py:699-701), O += P V.
+// The warps' partial results are merged through shared memory at the end.  Lengths are read from
+// device memory, per row, so one captured launch serves every step (fused.py:262-271).
+#include "common.cuh"
+
+#define DM_WARPS 4
+#define DM_THREADS (DM_WARPS * 32)
+#define DM_STAGES 3
+#define DM_ROWS 16
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <int D> __device__ __forceinline__ int tile_offset(int row, int chunk) {
+  constexpr int C = D / 8;
+  const int sw = C >= 8 ? (row & 7) : ((row / (8 / C)) % C);
+  return row * D * 2 + ((chunk ^ sw) << 4);
+}
+
+template <int D>
+__global__ void __launch_bounds__(DM_THREADS)
+attention_decode_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out,
+                            const bf16* __restrict__ k_store, const bf16* __restrict__ v_store,
+                            const int* __restrict__ block_table, int table_stride,
+                            const int* __restrict__ row_slot, const int* __restrict__ row_kv_len,
+                            int heads, int kv_heads, float scale_log2, int window, int n_splits,
+                            float* __restrict__ part_acc, float* __restrict__ part_ml) {
+  constexpr int C = D / 8;
+  constexpr int PAGE_BYTES = SB_PAGE_TOKENS * D * 2;
+  constexpr int STAGE_BYTES = 2 * PAGE_BYTES;
+  constexpr int KSTEPS = D / 16;
+  constexpr int NBLK = D / 8;
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* q_tile = smem;                          // [16][D] bfloat16
+  uint8_t* ring = smem + DM_ROWS * D * 2;          // DM_STAGES x (keys, values)
+  __shared__ float sh_m[DM_WARPS][DM_ROWS], sh_l[DM_WARPS][DM_ROWS];
+
+  const int groups = heads / kv_heads;
+  const int chunks = (groups + DM_ROWS - 1) / DM_ROWS;
+  const int row = blockIdx.x;
+  const int kvh = blockIdx.y / chunks;
+  const int g0 = (blockIdx.y % chunks) * DM_ROWS;
+  const int gc = min(DM_ROWS, groups - g0);
+  const int split = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  const int kv_len = row_kv_len[row];
+  int first = 0;
+  if (window > 0 && kv_len - window > 0) first = kv_len - window;
+  const int first_page = first / SB_PAGE_TOKENS;
+  const int end_page = (kv_len + SB_PAGE_TOKENS - 1) / SB_PAGE_TOKENS;
+  const int per_split = (end_page - first_page + n_splits - 1) / n_splits;
+  const int p_begin = first_page + split * per_split;
+  const int p_end = min(p_begin + per_split, end_page);
+  const int n_pages = max(p_end - p_begin, 0);
+  const int* pages = block_table + (size_t)row_slot[row] * table_stride;
+
+  // ---- the group's queries: row r of the tile is head g0 + r; rows past the group are zero
+  for (int idx = tid; idx < DM_ROWS * C; idx += DM_THREADS) {
+    const int r = idx / C, c = idx % C;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < gc) v = *reinterpret_cast<const uint4*>(q + ((size_t)row * heads + (size_t)kvh * groups + g0 + r) * D + c * 8);
+    *reinterpret_cast<uint4*>(q_tile + tile_offset<D>(r, c)) = v;
+  }
+  auto load_page = [&](int i) {
+    if (i < n_pages) {
+      const size_t base = page_row(pages[p_begin + i], kvh, 0, kv_heads, D);
+      uint8_t* dst = ring + (size_t)(i % DM_STAGES) * STAGE_BYTES;
+      for (int idx = tid; idx < SB_PAGE_TOKENS * C; idx += DM_THREADS) {
+        const int r = idx / C, c = idx % C;
+        cp_async16(dst + tile_offset<D>(r, c), k_store + base + (size_t)idx * 8);
+        cp_async16(dst + PAGE_BYTES + tile_offset<D>(r, c), v_store + base + (size_t)idx * 8);
+      }
+    }
+    cp_commit();
+  };
+#pragma unroll
+  for (int i = 0; i < DM_STAGES - 1; ++i) load_page(i);
+  __syncthreads();  // the query tile is written
+
+  uint32_t qf[KSTEPS][4];
+  {
+    const int r = (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk)
+      ldmatrix_x4(smem_u32(q_tile + tile_offset<D>(r, 2 * kk + (lane >> 4))), qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
+  }
+  float o[NBLK][4];
+#pragma unroll
+  for (int n = 0; n < NBLK; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+  for (int i = 0; i < n_pages; ++i) {
+    load_page(i + DM_STAGES - 1);     // its stage was released by the barrier that ended page i - 1
+    cp_wait<DM_STAGES - 1>();         // page i has landed (for this thread's copies)
+    __syncthreads();                  // ... and for everyone's
+    const uint8_t* kt = ring + (size_t)(i % DM_STAGES) * STAGE_BYTES;
+    const uint8_t* vt = kt + PAGE_BYTES;
+    const int j0 = (p_begin + i) * SB_PAGE_TOKENS + warp * 16;   // this warp's 16 keys
+
+    float s[2][4];
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+      uint32_t b0, b1, b2, b3;
+      const int key = warp * 16 + (lane & 7) + (lane >> 4) * 8;
+      ldmatrix_x4(smem_u32(kt + tile_offset<D>(key, 2 * kk + ((lane >> 3) & 1))), b0, b1, b2, b3);
+      mma_bf16(s[0], qf[kk], b0, b1);
+      mma_bf16(s[1], qf[kk], b2, b3);
+    }
+    const bool edge = j0 < first || j0 + 16 > kv_len;
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float v = s[nb][e] * scale_log2;
+        if (edge) {
+          const int j = j0 + nb * 8 + (lane & 3) * 2 + (e & 1);
+          if (j < first || j >= kv_len) v = -INFINITY;
+        }
+        s[nb][e] = v;
+        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      }
+    }
+    float alpha[2], m_use[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      const float m_new = fmaxf(m_run[h], mx[h]);
+      m_use[h] = m_new == -INFINITY ? 0.f : m_new;
+      alpha[h] = exp2f(m_run[h] - m_use[h]);
+      m_run[h] = m_new;
+    }
+    uint32_t pf[4];
+    {
+      const float p00 = exp2f(s[0][0] - m_use[0]), p01 = exp2f(s[0][1] - m_use[0]);
+      const float p02 = exp2f(s[0][2] - m_use[1]), p03 = exp2f(s[0][3] - m_use[1]);
+      const float p10 = exp2f(s[1][0] - m_use[0]), p11 = exp2f(s[1][1] - m_use[0]);
+      const float p12 = exp2f(s[1][2] - m_use[1]), p13 = exp2f(s[1][3] - m_use[1]);
+      l_run[0] = l_run[0] * alpha[0] + (p00 + p01 + p10 + p11);
+      l_run[1] = l_run[1] * alpha[1] + (p02 + p03 + p12 + p13);
+      pf[0] = pack_bf16(p00, p01); pf[1] = pack_bf16(p02, p03);
+      pf[2] = pack_bf16(p10, p11); pf[3] = pack_bf16(p12, p13);
+    }
+#pragma unroll
+    for (int n = 0; n < NBLK; n += 2) {
+      o[n][0] *= alpha[0]; o[n][1] *= alpha[0]; o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
+      o[n + 1][0] *= alpha[0]; o[n + 1][1] *= alpha[0]; o[n + 1][2] *= alpha[1]; o[n + 1][3] *= alpha[1];
+      uint32_t b0, b1, b2, b3;
+      const int key = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+      ldmatrix_x4_trans(smem_u32(vt + tile_offset<D>(key, n + (lane >> 4))), b0, b1, b2, b3);
+      mma_bf16(o[n], pf, b0, b1);
+      mma_bf16(o[n + 1], pf, b2, b3);
+    }
+    __syncthreads();  // everyone is done with this stage; the next iteration refills it
+  }
+  cp_wait<0>();
+  __syncthreads();
+
+  // ---- merge the four warps (each saw different keys) through shared memory
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+  }
+  float* sh_o = reinterpret_cast<float*>(ring);    // [warps][16][D] floats, the ring is free now
+  const int r_a = lane >> 2;
+  if ((lane & 3) == 0) {
+    sh_m[warp][r_a] = m_run[0]; sh_m[warp][r_a + 8] = m_run[1];
+    sh_l[warp][r_a] = l_run[0]; sh_l[warp][r_a + 8] = l_run[1];
+  }
+#pragma unroll
+  for (int n = 0; n < NBLK; ++n) {
+    const int col = n * 8 + (lane & 3) * 2;
+    float* base = sh_o + ((size_t)warp * DM_ROWS) * D;
+    base[(size_t)r_a * D + col] = o[n][0];
+    base[(size_t)r_a * D + col + 1] = o[n][1];
+    base[(size_t)(r_a + 8) * D + col] = o[n][2];
+    base[(size_t)(r_a + 8) * D + col + 1] = o[n][3];
+  }
+  __syncthreads();
+  for (int idx = tid; idx < gc * D; idx += DM_THREADS) {
+    const int r = idx / D, d = idx - r * D;
+    float m_all = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DM_WARPS; ++w) m_all = fmaxf(m_all, sh_m[w][r]);
+    float lsum = 0.f, a = 0.f;
+#pragma unroll
+    for (int w = 0; w < DM_WARPS; ++w) {
+      const float wgt = sh_m[w][r] == -INFINITY ? 0.f : exp2f(sh_m[w][r] - m_all);
+      lsum += sh_l[w][r] * wgt;
+      a += sh_o[((size_t)w * DM_ROWS + r) * D + d] * wgt;
+    }
+    const int head = kvh * groups + g0 + r;
+    if (n_splits == 1) {
+      out[((size_t)row * heads + head) * D + d] = __float2bfloat16_rn(a / lsum);
+    } else {
+      const size_t slot = ((size_t)row * heads + head) * n_splits + split;
+      part_acc[slot * D + d] = a;
+      if (d == 0) { part_ml[slot * 2] = m_all; part_ml[slot * 2 + 1] = lsum; }
+    }
+  }
+}
+
+// out[row, head, :] = sum_s w_s acc_s / sum_s w_s l_s with w_s = 2^(m_s - max m)
+__global__ void attention_merge_mma_kernel(const float* __restrict__ part_acc,
+                                           const float* __restrict__ part_ml, bf16* __restrict__ out,
+                                           int n_splits, int head_dim) {
+  const size_t rh = blockIdx.x;
+  float m_all = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) m_all = fmaxf(m_all, part_ml[(rh * n_splits + s) * 2]);
+  float lsum = 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float ms = part_ml[(rh * n_splits + s) * 2];
+    if (ms != -INFINITY) lsum += part_ml[(rh * n_splits + s) * 2 + 1] * exp2f(ms - m_all);
+  }
+  for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float ms = part_ml[(rh * n_splits + s) * 2];
+      if (ms != -INFINITY) a += part_acc[(rh * n_splits + s) * head_dim + d] * exp2f(ms - m_all);
+    }
+    out[rh * head_dim + d] = __float2bfloat16_rn(a / lsum);
+  }
+}
+
+template <int D>
+static int launch(const void* q, void* out, const void* k_store, const void* v_store,
+                  const int* block_table, int table_stride, const int* row_slot, const int* row_kv_len,
+                  int rows, int heads, int kv_heads, float scale, int window, int n_splits,
+                  float* part_acc, float* part_ml, cudaStream_t s) {
+  // queries + ring; the ring is reused for the warps' float partial results at the end
+  constexpr int RING = DM_STAGES * 2 * SB_PAGE_TOKENS * D * 2;
+  constexpr int MERGE = DM_WARPS * DM_ROWS * D * 4;
+  const int smem = DM_ROWS * D * 2 + (RING > MERGE ? RING : MERGE);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int groups = heads / kv_heads;
+  const int chunks = (groups + DM_ROWS - 1) / DM_ROWS;
+  dim3 grid(rows, kv_heads * chunks, n_splits);
+  attention_decode_mma_kernel<D><<<grid, DM_THREADS, smem, s>>>(
+      (const bf16*)q, (bf16*)out, (const bf16*)k_store, (const bf16*)v_store, block_table, table_stride,
+      row_slot, row_kv_len, heads, kv_heads, scale * 1.4426950408889634f, window, n_splits, part_acc,
+      part_ml);
+  int rc = SB_LAUNCH_RESULT();
+  if (rc || n_splits == 1) return rc;
+  attention_merge_mma_kernel<<<rows * heads, D < 128 ? D : 128, 0, s>>>(part_acc, part_ml, (bf16*)out,
+                                                                       n_splits, D);
+  return SB_LAUNCH_RESULT();
+}
+
+extern "C" {
+
+// Same contract as sb_attention_decode, bfloat16 only; head_dim 16, 32, 64 or 128 (-2 otherwise).
+int sb_attention_decode_mma(const void* q, void* out, const void* k_store, const void* v_store,
+                            const int* block_table, int table_stride, const int* row_slot,
+                            const int* row_kv_len, int rows, int heads, int kv_heads, int head_dim,
+                            float scale, int window, int n_splits, float* part_acc, float* part_ml,
+                            cudaStream_t s) {
+  if (rows == 0) return 0;
+  if (kv_heads <= 0 || heads % kv_heads || n_splits < 1) return -2;
+#define ARGS q, out, k_store, v_store, block_table, table_stride, row_slot, row_kv_len, rows, heads, \
+             kv_heads, scale, window, n_splits, part_acc, part_ml, s
+  switch (head_dim) {
+    case 16: return launch<16>(ARGS);
+    case 32: return launch<32>(ARGS);
+    case 64: return launch<64>(ARGS);
+    case 128: return launch<128>(ARGS);
+    default: return -2;
+  }
+#undef ARGS
+}
+
+}  // extern "C"

@@ -35,6 +35,7 @@ SOURCES = (
     "rope_cache",
     "attention_rowwise",
     "attention_decode",
+    "attention_decode_mma",
     "attention_prefill",
     "linear_small",
     "sgemm",

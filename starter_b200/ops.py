@@ -359,10 +359,10 @@ def decode_attention_takes(head_dim: int, dtype) -> bool:
     return head_dim in DECODE_HEAD_DIMS and head_dim * dtype.itemsize <= 512
 
 
-def decode_splits(rows: int, kv_heads: int, groups: int) -> int:
+def decode_splits(rows: int, kv_heads: int, groups: int, group_rows: int = 4) -> int:
     """How many parts to cut each row's keys into: as many as keep all blocks resident at once
     (two per SM), so that no block waits for a second wave."""
-    blocks = rows * kv_heads * ((groups + 3) // 4)
+    blocks = rows * kv_heads * (-(-groups // group_rows))
     return max(1, min(32, (2 * 148) // blocks))
 
 
@@ -388,18 +388,25 @@ def attention_decode(q, k_store, v_store, block_table, row_slot, row_kv_len, hea
     _need(block_table, "block_table", torch.int32, 2)
     _need(row_slot, "row_slot", torch.int32, 1)
     _need(row_kv_len, "row_kv_len", torch.int32, 1)
+    tensor_cores = q.dtype == torch.bfloat16 and head_dim in PREFILL_HEAD_DIMS
     if n_splits is None:
-        n_splits = decode_splits(rows, kv_heads, heads // kv_heads)
+        n_splits = decode_splits(rows, kv_heads, heads // kv_heads, 16 if tensor_cores else 4)
     out = torch.empty_like(q)
     part_acc = part_ml = None
     if n_splits > 1:
         part_acc = torch.empty((rows * heads * n_splits * head_dim,), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((rows * heads * n_splits * 2,), dtype=torch.float32, device=q.device)
-    rc = build.load("attention_decode").sb_attention_decode(
-        _code(q.dtype), _ptr(q), _ptr(out), _ptr(k_store), _ptr(v_store), _ptr(block_table),
-        block_table.shape[1], _ptr(row_slot), _ptr(row_kv_len), rows, heads, kv_heads, head_dim,
-        ctypes.c_float(scale), int(window or 0), n_splits, _ptr(part_acc), _ptr(part_ml),
-        _ptr(status), _stream())
+    if tensor_cores:
+        rc = build.load("attention_decode_mma").sb_attention_decode_mma(
+            _ptr(q), _ptr(out), _ptr(k_store), _ptr(v_store), _ptr(block_table), block_table.shape[1],
+            _ptr(row_slot), _ptr(row_kv_len), rows, heads, kv_heads, head_dim, ctypes.c_float(scale),
+            int(window or 0), n_splits, _ptr(part_acc), _ptr(part_ml), _stream())
+    else:
+        rc = build.load("attention_decode").sb_attention_decode(
+            _code(q.dtype), _ptr(q), _ptr(out), _ptr(k_store), _ptr(v_store), _ptr(block_table),
+            block_table.shape[1], _ptr(row_slot), _ptr(row_kv_len), rows, heads, kv_heads, head_dim,
+            ctypes.c_float(scale), int(window or 0), n_splits, _ptr(part_acc), _ptr(part_ml),
+            _ptr(status), _stream())
     _check(rc, "attention_decode")
     return out
 
