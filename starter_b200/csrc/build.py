@@ -36,6 +36,7 @@ SOURCES = (
     "attention_rowwise",
     "attention_decode",
     "attention_decode_mma",
+    "attention_decode_noalloc",
     "attention_prefill",
     "linear_small",
     "sgemm",
@@ -88,10 +89,21 @@ def _headers() -> list:
     return sorted(f for f in os.listdir(HERE) if f.endswith((".cuh", ".h")))
 
 
+def _included_sources(name: str) -> list:
+    """Other ``.cu`` files of this folder that ``name.cu`` includes."""
+    found = []
+    with open(os.path.join(HERE, name + ".cu"), "r", encoding="utf-8") as handle:
+        for line in handle:
+            line = line.strip()
+            if line.startswith("#include \"") and line.endswith(".cu\""):
+                found.append(line[len("#include \""):-1])
+    return found
+
+
 def _digest(name: str) -> str:
     h = hashlib.sha256()
     h.update(" ".join(NVCC_FLAGS).encode())
-    for fname in [name + ".cu"] + _headers():
+    for fname in [name + ".cu"] + _included_sources(name) + _headers():
         with open(os.path.join(HERE, fname), "rb") as handle:
             h.update(fname.encode())
             h.update(handle.read())
