@@ -67,6 +67,8 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out,
   uint8_t* ring = smem + DM_ROWS * D * 2;          // DM_STAGES x (keys, values)
   __shared__ float sh_m[DM_WARPS][DM_ROWS], sh_l[DM_WARPS][DM_ROWS];
 
+  pdl_trigger();
+  pdl_wait();
   const int groups = heads / kv_heads;
   const int chunks = (groups + DM_ROWS - 1) / DM_ROWS;
   const int row = blockIdx.x;
@@ -241,6 +243,8 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out,
 __global__ void attention_merge_mma_kernel(const float* __restrict__ part_acc,
                                            const float* __restrict__ part_ml, bf16* __restrict__ out,
                                            int n_splits, int head_dim) {
+  pdl_trigger();
+  pdl_wait();
   const size_t rh = blockIdx.x;
   float m_all = -INFINITY;
   for (int s = 0; s < n_splits; ++s) m_all = fmaxf(m_all, part_ml[(rh * n_splits + s) * 2]);
@@ -277,15 +281,13 @@ static int launch(const void* q, void* out, const void* k_store, const void* v_s
   const int groups = heads / kv_heads;
   const int chunks = (groups + DM_ROWS - 1) / DM_ROWS;
   dim3 grid(rows, kv_heads * chunks, n_splits);
-  attention_decode_mma_kernel<D><<<grid, DM_THREADS, smem, s>>>(
+  int rc = launch_dependent(attention_decode_mma_kernel<D>, grid, dim3(DM_THREADS), smem, s,
       (const bf16*)q, (bf16*)out, (const bf16*)k_store, (const bf16*)v_store, block_table, table_stride,
       row_slot, row_kv_len, heads, kv_heads, scale * 1.4426950408889634f, window, n_splits, part_acc,
       part_ml);
-  int rc = SB_LAUNCH_RESULT();
   if (rc || n_splits == 1) return rc;
-  attention_merge_mma_kernel<<<rows * heads, D < 128 ? D : 128, 0, s>>>(part_acc, part_ml, (bf16*)out,
-                                                                       n_splits, D);
-  return SB_LAUNCH_RESULT();
+  return launch_dependent(attention_merge_mma_kernel, dim3(rows * heads), dim3(D < 128 ? D : 128), 0, s,
+                          (const float*)part_acc, (const float*)part_ml, (bf16*)out, n_splits, D);
 }
 
 extern "C" {

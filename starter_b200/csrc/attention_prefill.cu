@@ -69,6 +69,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out,
   uint8_t* k_tiles = smem + PF_BQ * D * 2;      // 2 x [64][D]
   uint8_t* v_tiles = k_tiles + 2 * TILE_BYTES;  // 2 x [64][D]
 
+  pdl_trigger();
+  pdl_wait();
   const int tile = blockIdx.x, head = blockIdx.y;
   const int seq = tile_seq[tile];
   const int q_first = tile_first[tile];         // first query of this tile within the step's tokens of seq
@@ -248,11 +250,10 @@ static int launch(const void* q, void* out, const void* k_store, const void* v_s
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  attention_prefill_kernel<D><<<dim3(n_tiles, heads), PF_THREADS, smem, s>>>(
+  return launch_dependent(attention_prefill_kernel<D>, dim3(n_tiles, heads), dim3(PF_THREADS), smem, s,
       (const bf16*)q, (bf16*)out, (const bf16*)k_store, (const bf16*)v_store, block_table, table_stride,
       seq_slot, seq_q_start, seq_q_len, seq_kv_len, tile_seq, tile_first, heads, kv_heads,
       scale * 1.4426950408889634f, window);
-  return SB_LAUNCH_RESULT();
 }
 
 extern "C" {

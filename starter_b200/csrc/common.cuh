@@ -64,3 +64,34 @@ __device__ __forceinline__ size_t page_row(int page, int head, int offset, int k
 }
 
 #define SB_LAUNCH_RESULT() ((int)cudaGetLastError())
+
+// ---------------------------------------------------------------------------------- dependent launch
+// Kernels of a step run back to back on one stream and each is short, so the gap between one
+// kernel's last block and the next kernel's first instruction matters.  Launched with
+// launch_dependent(), a kernel may start while its predecessor is still running (as soon as every
+// block of the predecessor has called pdl_trigger() or exited), do whatever does not depend on the
+// predecessor (set up barriers, allocate tensor memory, prefetch WEIGHTS), and then call pdl_wait(),
+// which returns once the predecessor has completed and its writes are visible.
+//
+// The rule that keeps this safe: every kernel calls pdl_wait() before its first read of anything an
+// earlier kernel of the stream may have written and before its first write to global memory (a
+// buffer may be recycled memory that an earlier kernel still reads).  Because a kernel cannot
+// complete before its own pdl_wait() returns, completion is transitive along the stream.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... Params, typename... Args>
+static inline int launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                                   cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}

@@ -11,6 +11,8 @@
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
                                  T* __restrict__ out, int hidden, int vocab, int* status) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   int tok = tokens[row];
   const bool bad = tok < 0 || tok >= vocab;
@@ -33,6 +35,8 @@ __global__ void rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delta,
                                const W* __restrict__ gain, T* __restrict__ y,
                                const int* __restrict__ rows, int hidden, float eps) {
   __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
   const int out_row = blockIdx.x;
   const int in_row = rows ? rows[out_row] : out_row;
   T* xr = x + (size_t)in_row * hidden;
@@ -67,12 +71,10 @@ static int launch_rmsnorm(void* x, const void* delta, const void* gain, void* y,
   const W* gp = (const W*)gain;
   T* yp = (T*)y;
   if (delta && !rows)
-    rmsnorm_kernel<T, W, true, true><<<n_rows, threads, 0, s>>>(xp, dp, gp, yp, rows, hidden, eps);
-  else if (delta)
-    rmsnorm_kernel<T, W, true, false><<<n_rows, threads, 0, s>>>(xp, dp, gp, yp, rows, hidden, eps);
-  else
-    rmsnorm_kernel<T, W, false, false><<<n_rows, threads, 0, s>>>(xp, dp, gp, yp, rows, hidden, eps);
-  return SB_LAUNCH_RESULT();
+    return launch_dependent(rmsnorm_kernel<T, W, true, true>, dim3(n_rows), dim3(threads), 0, s, xp, dp, gp, yp, rows, hidden, eps);
+  if (delta)
+    return launch_dependent(rmsnorm_kernel<T, W, true, false>, dim3(n_rows), dim3(threads), 0, s, xp, dp, gp, yp, rows, hidden, eps);
+  return launch_dependent(rmsnorm_kernel<T, W, false, false>, dim3(n_rows), dim3(threads), 0, s, xp, dp, gp, yp, rows, hidden, eps);
 }
 
 // ------------------------------------------------------------------------------------ gated activation
@@ -80,6 +82,8 @@ static int launch_rmsnorm(void* x, const void* delta, const void* gain, void* y,
 // act[r, c] = round(silu(gate)) * up with gate = gu[r, c], up = gu[r, inner + c].
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, int inner, size_t total) {
+  pdl_trigger();
+  pdl_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (; i < total; i += stride) {
@@ -100,10 +104,8 @@ int sb_embedding(int dtype, const int* tokens, const void* table, void* out, int
   if (n_tokens == 0) return 0;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (dtype == 0)
-    embedding_kernel<float><<<n_tokens, threads, 0, s>>>(tokens, (const float*)table, (float*)out, hidden, vocab, status);
-  else
-    embedding_kernel<bf16><<<n_tokens, threads, 0, s>>>(tokens, (const bf16*)table, (bf16*)out, hidden, vocab, status);
-  return SB_LAUNCH_RESULT();
+    return launch_dependent(embedding_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, tokens, (const float*)table, (float*)out, hidden, vocab, status);
+  return launch_dependent(embedding_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, s, tokens, (const bf16*)table, (bf16*)out, hidden, vocab, status);
 }
 
 // x: [*, hidden] read (and, with delta and without rows, updated in place); y: [n_rows, hidden].
@@ -122,10 +124,8 @@ int sb_swiglu(int dtype, const void* gu, void* act, int n_rows, int inner, cudaS
   size_t blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (dtype == 0)
-    swiglu_kernel<float><<<(int)blocks, threads, 0, s>>>((const float*)gu, (float*)act, inner, total);
-  else
-    swiglu_kernel<bf16><<<(int)blocks, threads, 0, s>>>((const bf16*)gu, (bf16*)act, inner, total);
-  return SB_LAUNCH_RESULT();
+    return launch_dependent(swiglu_kernel<float>, dim3((int)blocks), dim3(threads), 0, s, (const float*)gu, (float*)act, inner, total);
+  return launch_dependent(swiglu_kernel<bf16>, dim3((int)blocks), dim3(threads), 0, s, (const bf16*)gu, (bf16*)act, inner, total);
 }
 
 }  // extern "C"

@@ -126,7 +126,7 @@ __device__ __forceinline__ uint32_t instr_desc(int bm) {
 
 struct GemmArgs {
   void* out;            // [rows, n_out] bfloat16 or float
-  float* scratch;       // [splits][tiles][TILE_N][bm] float partial tiles (splits > 1 or gated)
+  float* scratch;       // [splits][tiles][TILE_N][bm] float partial tiles (splits > 1)
   int* counters;        // one per (m tile, n tile), zero between launches
   int* status;
   int rows, n_out, k_dim;
@@ -168,6 +168,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     last_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  pdl_trigger();
   if (warp == 1) tmem_alloc(&tmem_holder, TMEM_COLS);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -179,9 +180,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     // ---------------- producer: one lane feeds the ring
     if (lane == 0) {
       int issued = 0;
-      for (int i = 0; i < n_kb; ++i) {
+      // the weights do not depend on the kernels before this one: the first stages' weight tiles are
+      // on their way before the predecessor has finished; the activations follow after the wait
+      const int early = min(n_kb, STAGES);
+      for (int i = 0; i < early; ++i) {
+        uint8_t* a = smem + (size_t)i * STAGE_BYTES;
+        mbar_expect_tx(&full_bar[i], STAGE_BYTES);
+        const int k = (kb_begin + i) * TILE_K;
+        tma_load_2d(a, &map_w, &full_bar[i], k, row_a);
+        tma_load_2d(a + HALF_BYTES, &map_w, &full_bar[i], k, row_b);
+      }
+      pdl_wait();
+      for (int i = 0; i < early; ++i)
+        tma_load_2d(smem + (size_t)i * STAGE_BYTES + A_BYTES, &map_x, &full_bar[i], (kb_begin + i) * TILE_K, m0);
+      issued = early;
+      for (int i = early; i < n_kb; ++i) {
         const int s = i % STAGES;
-        if (i >= STAGES && !mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, abort)) break;
+        if (!mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, abort)) break;
         uint8_t* a = smem + (size_t)s * STAGE_BYTES;
         mbar_expect_tx(&full_bar[s], STAGE_BYTES);
         const int k = (kb_begin + i) * TILE_K;
@@ -223,13 +238,46 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     // ---------------- epilogue: warps 2..5 own the TMEM lane quarters 2, 3, 0, 1
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;                 // row of the tile = TMEM lane
+    pdl_wait();   // before the first store: the output may be memory an earlier kernel still reads
     const bool have = n_kb > 0 && mbar_wait(&acc_bar, 0, abort);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const int rows_here = min(BM, args.rows - m0);
-    const bool direct = args.splits == 1 && !args.gated;
+    const bool direct = args.splits == 1;
     const int n = tile * TILE_N + r;                   // output column when not gated
     float* part = args.scratch + (((size_t)(mtile * gridDim.y + split) * n_tiles + tile) * TILE_N + r) * BM;
-    if (have || n_kb == 0) {
+    if (direct && args.gated) {
+      // rows 0..63 of the tile are gate rows, 64..127 the matching up rows: the warps that hold the
+      // up rows hand them over through shared memory (the ring is idle once the accumulator is
+      // complete), column-major so that neither side has bank conflicts
+      float* up_sm = reinterpret_cast<float*>(smem);   // [BM][64]
+      if (r >= 64 && have) {
+#pragma unroll 1
+        for (int c = 0; c < BM; c += 8) {
+          float v[8];
+          tmem_load8(tmem + ((uint32_t)(quarter * 32) << 16) + c, v);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) up_sm[(c + j) * 64 + (r - 64)] = v[j];
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const int ncol = tile * 64 + r;
+      if (r < 64 && have && ncol < args.n_out) {
+#pragma unroll 1
+        for (int c = 0; c < BM; c += 8) {
+          float v[8];
+          tmem_load8(tmem + ((uint32_t)(quarter * 32) << 16) + c, v);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int m = c + j;
+            if (m < rows_here) {
+              const float gr = rnd<bf16>(v[j]), ur = rnd<bf16>(up_sm[m * 64 + r]);
+              const float y = rnd<bf16>(gr / (1.f + __expf(-gr))) * ur;
+              ((bf16*)args.out)[(size_t)(m0 + m) * args.n_out + ncol] = __float2bfloat16_rn(y);
+            }
+          }
+        }
+      }
+    } else if (have || n_kb == 0) {
 #pragma unroll 1
       for (int c = 0; c < BM; c += 8) {
         float v[8];
@@ -370,15 +418,14 @@ static int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const Gemm
     configured = true;
   }
   dim3 grid(tiles, args.splits, m_tiles);
-  gemm_tcgen05_kernel<BM><<<grid, GEMM_THREADS, smem, s>>>(map_w, map_x, args);
-  return SB_LAUNCH_RESULT();
+  return launch_dependent(gemm_tcgen05_kernel<BM>, grid, dim3(GEMM_THREADS), smem, s, map_w, map_x, args);
 }
 
 extern "C" {
 
 // Bytes of float scratch the call needs (0 when the result is written straight from tensor memory).
 long long sb_gemm_tcgen05_scratch(int rows, int n_out, int splits, int gated, int bm) {
-  if (splits == 1 && !gated) return 0;
+  if (splits == 1) return 0;
   const long long tiles = gated ? (n_out + 63) / 64 : (n_out + TILE_N - 1) / TILE_N;
   const long long m_tiles = (rows + bm - 1) / bm;
   return m_tiles * splits * tiles * TILE_N * bm * 4;

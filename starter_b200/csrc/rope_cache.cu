@@ -19,6 +19,8 @@ __global__ void qk_norm_rope_store_kernel(
     const int* __restrict__ tok_slot, const int* __restrict__ block_table, int table_stride,
     T* __restrict__ k_store, T* __restrict__ v_store, int n_tokens, int heads, int kv_heads,
     int head_dim, float eps, int heads_per_token, int row_stride) {
+  pdl_trigger();
+  pdl_wait();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp >= n_tokens * heads_per_token) return;
@@ -98,11 +100,10 @@ static int launch(const void* qkv, void* q_out, const void* q_gain, const void* 
   if (warps == 0) return 0;
   const int threads = 128;
   const long long blocks = (warps * 32 + threads - 1) / threads;
-  qk_norm_rope_store_kernel<T, W><<<(unsigned)blocks, threads, 0, s>>>(
+  return launch_dependent(qk_norm_rope_store_kernel<T, W>, dim3((unsigned)blocks), dim3(threads), 0, s,
       (const T*)qkv, (T*)q_out, (const W*)q_gain, (const W*)k_gain, cos_table, sin_table, tok_pos,
       tok_slot, block_table, table_stride, (T*)k_store, (T*)v_store, n_tokens, heads, kv_heads,
       head_dim, eps, per_token, row_stride);
-  return SB_LAUNCH_RESULT();
 }
 
 extern "C" {

@@ -55,6 +55,8 @@ __global__ void sample_chunk_kernel(const float* __restrict__ logits, int vocab,
                                     float* __restrict__ cand_v, int* __restrict__ cand_i) {
   __shared__ float sh_v[32];
   __shared__ int sh_i[32];
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.y, chunk = blockIdx.x;
   const float* lr = logits + (size_t)row * row_stride;
   const float t = temperature ? temperature[row] : 0.f;
@@ -87,6 +89,8 @@ __global__ void sample_pick_kernel(const float* __restrict__ cand_v, const int* 
                                    int* feed_token, int* feed_pos, int* feed_len) {
   __shared__ float sh_v[32];
   __shared__ int sh_i[32];
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   Best b = {-INFINITY, 0x7fffffff};
   for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
@@ -126,13 +130,11 @@ int sb_sample(const float* logits, int rows, int vocab, long long row_stride, co
               cudaStream_t s) {
   if (rows == 0) return 0;
   const int chunks = sb_sample_chunks(vocab);
-  sample_chunk_kernel<<<dim3(chunks, rows), 256, 0, s>>>(logits, vocab, (size_t)row_stride, temperature,
-                                                        request_key, position, cand_v, cand_i);
-  int rc = SB_LAUNCH_RESULT();
+  int rc = launch_dependent(sample_chunk_kernel, dim3(chunks, rows), dim3(256), 0, s, logits, vocab,
+                            (size_t)row_stride, temperature, request_key, position, cand_v, cand_i);
   if (rc) return rc;
-  sample_pick_kernel<<<rows, 128, 0, s>>>(cand_v, cand_i, chunks, vocab, out, status, feed_token,
-                                          feed_pos, feed_len);
-  return SB_LAUNCH_RESULT();
+  return launch_dependent(sample_pick_kernel, dim3(rows), dim3(128), 0, s, (const float*)cand_v,
+                          (const int*)cand_i, chunks, vocab, out, status, feed_token, feed_pos, feed_len);
 }
 
 }  // extern "C"
