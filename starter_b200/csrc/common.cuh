@@ -80,6 +80,27 @@ __device__ __forceinline__ size_t page_row(int page, int head, int offset, int k
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// The same, as thread-block clusters of `cluster` CTAs (every grid dimension a multiple of it).
+template <typename... Params, typename... Args>
+static inline int launch_dependent_cluster(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                                           cudaStream_t stream, dim3 cluster, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[2];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  attribute[1].id = cudaLaunchAttributeClusterDimension;
+  attribute[1].val.clusterDim.x = cluster.x;
+  attribute[1].val.clusterDim.y = cluster.y;
+  attribute[1].val.clusterDim.z = cluster.z;
+  config.attrs = attribute;
+  config.numAttrs = cluster.x * cluster.y * cluster.z > 1 ? 2 : 1;
+  return (int)cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
 template <typename... Params, typename... Args>
 static inline int launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
                                    cudaStream_t stream, Args... args) {

@@ -8,10 +8,11 @@
 // either matrix are zero-filled by TMA and masked on the way out, so no size needs padding.
 //
 // For a few rows the product is bound by reading w, and 128-row tiles alone would leave most SMs idle
-// (a 2560-row projection has 20), so the k range is cut into `splits` parts that run as separate CTAs.
-// Each writes its float partial tile to scratch; the last one to finish a tile (a counter per tile)
-// adds the parts in split order, so the sum does not depend on which CTA came last
-// (engine/kernels/fused.py:474-476), applies the epilogue and resets the counter.
+// (a 2560-row projection has 20), so the k range is cut into up to 8 `splits` that run as the CTAs of
+// one thread-block cluster.  Each CTA leaves its float partial tile in its own shared memory; after
+// a cluster barrier every CTA adds, for its share of the tile, the parts of all CTAs in split order
+// through distributed shared memory (so the sum does not depend on timing,
+// engine/kernels/fused.py:474-476) and applies the epilogue.  Nothing goes through global memory.
 //
 // With `gated`, w is [gate; up] stacked ([2 * n_out, k]); a tile holds 64 gate rows and the matching
 // 64 up rows and the epilogue writes round(silu(gate)) * up (fused.py:89-112).
@@ -27,7 +28,8 @@
 #define HALF_BYTES (64 * TILE_K * 2)
 #define A_BYTES (2 * HALF_BYTES)
 #define GEMM_THREADS 192
-#define GEMM_STAGES 4     // 74-98 KB of shared memory for bm <= 64: two or three CTAs share an SM
+#define GEMM_MAX_STAGES 8
+#define GEMM_MAX_SPLITS 8
 #define WAIT_LIMIT_NS 2000000000ull
 
 // ------------------------------------------------------------------------------------------ PTX
@@ -59,13 +61,19 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
 }
 
 // Bounded wait: false (and *abort set) if the phase did not complete in time or another role gave up.
+// The clock is looked at only now and then: reading it costs more than a try.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
-  if (mbar_try(bar, parity)) return true;
-  const uint64_t start = now_ns();
-  while (true) {
+#pragma unroll 1
+  for (int spin = 0; spin < 2048; ++spin)
     if (mbar_try(bar, parity)) return true;
-    if (*abort) return false;
-    if (now_ns() - start > WAIT_LIMIT_NS) { *abort = 1; return false; }
+  const uint64_t start = now_ns();
+#pragma unroll 1
+  for (uint32_t spin = 0;; ++spin) {
+    if (mbar_try(bar, parity)) return true;
+    if ((spin & 63) == 0) {
+      if (*abort) return false;
+      if (now_ns() - start > WAIT_LIMIT_NS) { *abort = 1; return false; }
+    }
   }
 }
 
@@ -124,13 +132,31 @@ __device__ __forceinline__ uint32_t instr_desc(int bm) {
 
 // ------------------------------------------------------------------------------------------ kernel
 
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// The address, in the cluster's shared window, of `addr` (an address of this CTA) in CTA `rank`.
+__device__ __forceinline__ uint32_t in_cta(uint32_t addr, uint32_t rank) {
+  uint32_t a;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(addr), "r"(rank));
+  return a;
+}
+__device__ __forceinline__ float ld_cluster(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+
 struct GemmArgs {
   void* out;            // [rows, n_out] bfloat16 or float
-  float* scratch;       // [splits][tiles][TILE_N][bm] float partial tiles (splits > 1)
-  int* counters;        // one per (m tile, n tile), zero between launches
   int* status;
   int rows, n_out, k_dim;
-  int splits, gated, out_float;
+  int splits, stages, gated, out_float;
 };
 
 template <int BM>
@@ -139,18 +165,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     const GemmArgs args) {
   constexpr int B_BYTES = BM * TILE_K * 2;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  constexpr int STAGES = GEMM_STAGES;
   constexpr uint32_t TMEM_COLS = BM < 32 ? 32 : BM;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
+  __shared__ uint64_t full_bar[GEMM_MAX_STAGES], empty_bar[GEMM_MAX_STAGES], acc_bar;
   __shared__ uint32_t tmem_holder;
-  __shared__ int abort_flag, last_flag;
+  __shared__ int abort_flag;
 
+  const int STAGES = args.stages;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = blockIdx.x, split = blockIdx.y, mtile = blockIdx.z;
-  const int n_tiles = gridDim.x;
   const int m0 = mtile * BM;
   const int kb_total = (args.k_dim + TILE_K - 1) / TILE_K;
   const int kb_per = (kb_total + args.splits - 1) / args.splits;
@@ -160,12 +185,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   // rows of w in the two 64-row halves of the tile
   const int row_a = args.gated ? tile * 64 : tile * TILE_N;
   const int row_b = args.gated ? args.n_out + tile * 64 : tile * TILE_N + 64;
+  const int rows_here = min(BM, args.rows - m0);
+  // the result goes straight from tensor memory to global memory unless parts must be added or
+  // gate and up rows (held by different threads) must meet
+  const bool staged = args.splits > 1 || args.gated;
+  float* part_sm = reinterpret_cast<float*>(smem);   // [BM][TILE_N] floats, in the idle ring
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     mbar_init(&acc_bar, 1);
     abort_flag = 0;
-    last_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   pdl_trigger();
@@ -217,11 +246,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     // ---------------- MMA issuer: one lane
     if (lane == 0) {
       const uint32_t idesc = instr_desc(BM);
-      bool ok = true;
-      for (int i = 0; i < n_kb && ok; ++i) {
+      for (int i = 0; i < n_kb; ++i) {
         const int s = i % STAGES;
-        ok = mbar_wait(&full_bar[s], (i / STAGES) & 1, abort);
-        if (!ok) break;
+        if (!mbar_wait(&full_bar[s], (i / STAGES) & 1, abort)) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
         const uint64_t a_desc = smem_desc(a_addr), b_desc = smem_desc(a_addr + A_BYTES);
@@ -235,135 +262,77 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       umma_commit(&acc_bar);
     }
   } else {
-    // ---------------- epilogue: warps 2..5 own the TMEM lane quarters 2, 3, 0, 1
+    // ---------------- epilogue, first half: warps 2..5 own the TMEM lane quarters 2, 3, 0, 1
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;                 // row of the tile = TMEM lane
     pdl_wait();   // before the first store: the output may be memory an earlier kernel still reads
     const bool have = n_kb > 0 && mbar_wait(&acc_bar, 0, abort);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const int rows_here = min(BM, args.rows - m0);
-    const bool direct = args.splits == 1;
     const int n = tile * TILE_N + r;                   // output column when not gated
-    float* part = args.scratch + (((size_t)(mtile * gridDim.y + split) * n_tiles + tile) * TILE_N + r) * BM;
-    if (direct && args.gated) {
-      // rows 0..63 of the tile are gate rows, 64..127 the matching up rows: the warps that hold the
-      // up rows hand them over through shared memory (the ring is idle once the accumulator is
-      // complete), column-major so that neither side has bank conflicts
-      float* up_sm = reinterpret_cast<float*>(smem);   // [BM][64]
-      if (r >= 64 && have) {
 #pragma unroll 1
-        for (int c = 0; c < BM; c += 8) {
-          float v[8];
-          tmem_load8(tmem + ((uint32_t)(quarter * 32) << 16) + c, v);
+    for (int c = 0; c < rows_here; c += 8) {
+      float v[8];
+      if (have) tmem_load8(tmem + ((uint32_t)(quarter * 32) << 16) + c, v);
+      else {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) up_sm[(c + j) * 64 + (r - 64)] = v[j];
-        }
+        for (int j = 0; j < 8; ++j) v[j] = 0.f;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      const int ncol = tile * 64 + r;
-      if (r < 64 && have && ncol < args.n_out) {
-#pragma unroll 1
-        for (int c = 0; c < BM; c += 8) {
-          float v[8];
-          tmem_load8(tmem + ((uint32_t)(quarter * 32) << 16) + c, v);
+      if (staged) {
+        // column-major, so that consecutive threads write consecutive words
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int m = c + j;
-            if (m < rows_here) {
-              const float gr = rnd<bf16>(v[j]), ur = rnd<bf16>(up_sm[m * 64 + r]);
-              const float y = rnd<bf16>(gr / (1.f + __expf(-gr))) * ur;
-              ((bf16*)args.out)[(size_t)(m0 + m) * args.n_out + ncol] = __float2bfloat16_rn(y);
-            }
-          }
-        }
-      }
-    } else if (have || n_kb == 0) {
-#pragma unroll 1
-      for (int c = 0; c < BM; c += 8) {
-        float v[8];
-        if (have) tmem_load8(tmem + ((uint32_t)(quarter * 32) << 16) + c, v);
-        else {
+        for (int j = 0; j < 8; ++j) part_sm[(c + j) * TILE_N + r] = v[j];
+      } else if (n < args.n_out) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) v[j] = 0.f;
-        }
-        if (direct) {
-          if (n < args.n_out) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const int m = c + j;
-              if (m < rows_here) {
-                const size_t at = (size_t)(m0 + m) * args.n_out + n;
-                if (args.out_float) ((float*)args.out)[at] = v[j];
-                else ((bf16*)args.out)[at] = __float2bfloat16_rn(v[j]);
-              }
-            }
-          }
-        } else {
-          *reinterpret_cast<float4*>(part + c) = make_float4(v[0], v[1], v[2], v[3]);
-          *reinterpret_cast<float4*>(part + c + 4) = make_float4(v[4], v[5], v[6], v[7]);
-        }
-      }
-    }
-    if (!direct) {
-      // publish the partial tile, then the last CTA of this tile adds the parts in split order
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (threadIdx.x == 64) {
-        const int ticket = atomicAdd(&args.counters[mtile * n_tiles + tile], 1);
-        last_flag = ticket == args.splits - 1;
-        if (last_flag) args.counters[mtile * n_tiles + tile] = 0;
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (last_flag && !*abort) {
-        __threadfence();
-        const int t = threadIdx.x - 64;                // 0..127
-        const float* base = args.scratch + ((size_t)(mtile * gridDim.y) * n_tiles + tile) * TILE_N * BM;
-        const size_t split_stride = (size_t)n_tiles * TILE_N * BM;
-        const int out_rows = args.gated ? 64 : TILE_N;
-        // an item is one output column and four activation rows; the loads of up to eight parts
-        // are in flight together and are added in split order
-        const int quads = (rows_here + 3) / 4;
-        for (int item = t; item < out_rows * quads; item += 128) {
-          const int orow = item % out_rows, m = (item / out_rows) * 4;
-          const int ncol = (args.gated ? tile * 64 : tile * TILE_N) + orow;
-          float4 g = make_float4(0.f, 0.f, 0.f, 0.f), u = g;
-          for (int s0 = 0; s0 < args.splits; s0 += 8) {
-            float4 gv[8], uv[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              if (s0 + j < args.splits) {
-                const float* p = base + (size_t)(s0 + j) * split_stride + (size_t)orow * BM + m;
-                gv[j] = __ldcg(reinterpret_cast<const float4*>(p));
-                if (args.gated) uv[j] = __ldcg(reinterpret_cast<const float4*>(p + 64 * BM));
-              }
-            }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              if (s0 + j < args.splits) {
-                g.x += gv[j].x; g.y += gv[j].y; g.z += gv[j].z; g.w += gv[j].w;
-                if (args.gated) { u.x += uv[j].x; u.y += uv[j].y; u.z += uv[j].z; u.w += uv[j].w; }
-              }
-            }
-          }
-          if (ncol < args.n_out) {
-            const float gs[4] = {g.x, g.y, g.z, g.w}, us[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if (m + j < rows_here) {
-                float y = gs[j];
-                if (args.gated) {
-                  const float gr = rnd<bf16>(gs[j]), ur = rnd<bf16>(us[j]);
-                  y = rnd<bf16>(gr / (1.f + __expf(-gr))) * ur;
-                }
-                const size_t at = (size_t)(m0 + m + j) * args.n_out + ncol;
-                if (args.out_float) ((float*)args.out)[at] = y;
-                else ((bf16*)args.out)[at] = __float2bfloat16_rn(y);
-              }
-            }
+        for (int j = 0; j < 8; ++j) {
+          const int m = c + j;
+          if (m < rows_here) {
+            const size_t at = (size_t)(m0 + m) * args.n_out + n;
+            if (args.out_float) ((float*)args.out)[at] = v[j];
+            else ((bf16*)args.out)[at] = __float2bfloat16_rn(v[j]);
           }
         }
       }
     }
+  }
+
+  // ---------------- epilogue, second half: add the parts of all splits and finish
+  if (staged) {
+    if (args.splits > 1) cluster_sync(); else __syncthreads();
+    if (warp >= 2 && !*abort) {
+      const uint32_t rank = args.splits > 1 ? cluster_rank() : 0;
+      const int out_rows = args.gated ? 64 : TILE_N;
+      const int n_chunks = out_rows / 32 * rows_here;   // a chunk: 32 consecutive outputs of one row
+      const uint32_t base = smem_u32(part_sm);
+      uint32_t remote[GEMM_MAX_SPLITS];
+#pragma unroll
+      for (int s = 0; s < GEMM_MAX_SPLITS; ++s) remote[s] = s < args.splits && args.splits > 1 ? in_cta(base, s) : base;
+      for (int ch = rank + args.splits * (warp - 2); ch < n_chunks; ch += args.splits * 4) {
+        const int m = ch * 32 / out_rows;
+        const int orow = ch * 32 % out_rows + lane;
+        const uint32_t at_g = (uint32_t)(m * TILE_N + orow) * 4;
+        float g = 0.f, u = 0.f;
+#pragma unroll
+        for (int s = 0; s < GEMM_MAX_SPLITS; ++s) {
+          if (s < args.splits) {
+            g += ld_cluster(remote[s] + at_g);
+            if (args.gated) u += ld_cluster(remote[s] + at_g + 64 * 4);
+          }
+        }
+        const int ncol = (args.gated ? tile * 64 : tile * TILE_N) + orow;
+        if (ncol < args.n_out) {
+          float y = g;
+          if (args.gated) {
+            const float gr = rnd<bf16>(g), ur = rnd<bf16>(u);
+            y = rnd<bf16>(gr / (1.f + __expf(-gr))) * ur;
+          }
+          const size_t at = (size_t)(m0 + m) * args.n_out + ncol;
+          if (args.out_float) ((float*)args.out)[at] = y;
+          else ((bf16*)args.out)[at] = __float2bfloat16_rn(y);
+        }
+      }
+    }
+    // nobody leaves (and gives up its shared memory) while a neighbour may still read it
+    if (args.splits > 1) cluster_sync();
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -409,37 +378,31 @@ template <int BM>
 static int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const GemmArgs& args, int tiles,
                   int m_tiles, cudaStream_t s) {
   constexpr int STAGE_BYTES = A_BYTES + BM * TILE_K * 2;
-  constexpr int STAGES = GEMM_STAGES;
-  const int smem = STAGES * STAGE_BYTES + 1024;
-  static bool configured = false;
-  if (!configured) {
+  const int smem = args.stages * STAGE_BYTES + 1024;
+  if (smem > 227 * 1024 || args.stages * STAGE_BYTES < BM * TILE_N * 4) return -2;
+  static int configured = 0;
+  if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BM>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured = smem;
   }
   dim3 grid(tiles, args.splits, m_tiles);
-  return launch_dependent(gemm_tcgen05_kernel<BM>, grid, dim3(GEMM_THREADS), smem, s, map_w, map_x, args);
+  return launch_dependent_cluster(gemm_tcgen05_kernel<BM>, grid, dim3(GEMM_THREADS), smem, s,
+                                  dim3(1, args.splits, 1), map_w, map_x, args);
 }
 
 extern "C" {
 
-// Bytes of float scratch the call needs (0 when the result is written straight from tensor memory).
-long long sb_gemm_tcgen05_scratch(int rows, int n_out, int splits, int gated, int bm) {
-  if (splits == 1) return 0;
-  const long long tiles = gated ? (n_out + 63) / 64 : (n_out + TILE_N - 1) / TILE_N;
-  const long long m_tiles = (rows + bm - 1) / bm;
-  return m_tiles * splits * tiles * TILE_N * bm * 4;
-}
-
 // x [rows, k_dim] and w [n_out (2 * n_out if gated), k_dim] bfloat16, row-major, 16-byte aligned,
-// k_dim a multiple of 8.  bm (16, 32, 64, 128 or 256) is the number of activation rows per tile.
-// counters: at least ceil(rows / bm) * tiles ints, zero on entry and zero again on exit.
+// k_dim a multiple of 8.  bm (16, 32, 64, 128 or 256) is the number of activation rows per tile,
+// splits (1..8) the number of CTAs that share a tile's k range, stages (2..8) the depth of the ring;
+// stages * (16 KB + bm * 128 B) must hold the bm x 128 float tile and fit in shared memory.
 // Returns -2 for sizes it does not take, -3/-4 if the tensor maps cannot be made.
 int sb_gemm_tcgen05(const void* x, const void* w, void* out, int rows, int n_out, int k_dim, int bm,
-                    int splits, int gated, int out_float, float* scratch, int* counters, int* status,
-                    cudaStream_t s) {
+                    int splits, int stages, int gated, int out_float, int* status, cudaStream_t s) {
   if (rows == 0 || n_out == 0) return 0;
-  if (k_dim % 8 || k_dim <= 0 || splits < 1) return -2;
+  if (k_dim % 8 || k_dim <= 0 || splits < 1 || splits > GEMM_MAX_SPLITS) return -2;
+  if (stages < 2 || stages > GEMM_MAX_STAGES) return -2;
   if (((uintptr_t)x | (uintptr_t)w) & 15) return -2;
   if (gated && n_out % 64) return -2;
   const int tiles = gated ? n_out / 64 : (n_out + TILE_N - 1) / TILE_N;
@@ -451,9 +414,9 @@ int sb_gemm_tcgen05(const void* x, const void* w, void* out, int rows, int n_out
   rc = make_map(&map_x, x, rows, k_dim, bm);
   if (rc) return rc;
   GemmArgs args;
-  args.out = out; args.scratch = scratch; args.counters = counters; args.status = status;
+  args.out = out; args.status = status;
   args.rows = rows; args.n_out = n_out; args.k_dim = k_dim;
-  args.splits = splits; args.gated = gated; args.out_float = out_float;
+  args.splits = splits; args.stages = stages; args.gated = gated; args.out_float = out_float;
   switch (bm) {
     case 16: return launch<16>(map_w, map_x, args, tiles, m_tiles, s);
     case 32: return launch<32>(map_w, map_x, args, tiles, m_tiles, s);

@@ -17,6 +17,11 @@ from .csrc import build
 
 PAGE_TOKENS = 64
 SMALL_ROWS = 16
+#: Up to this many rows the bfloat16 product runs on this library's tcgen05 kernel, where it is bound
+#: by streaming the weights; beyond it (prompts) the vendor's GEMM is used, as the reference does
+#: (engine/engine.py:431-450): the one-CTA 128 x 256 tile of the own kernel reaches about 60% of
+#: that library's throughput there.
+TENSOR_CORE_MAX_ROWS = 256
 MAX_HEAD_DIM = 256
 
 _DT = {torch.float32: 0, torch.bfloat16: 1}
@@ -149,7 +154,7 @@ def linear(x, weight, out_float=False, gated=False):
         raise KernelError(f"a gated weight needs an even number of rows, got {n_total}")
     n_out = n_total // 2 if gated else n_total
     dt = _code(x.dtype)
-    if dt == 1 and tensor_core_ok(x, weight, gated, n_out):
+    if dt == 1 and rows <= TENSOR_CORE_MAX_ROWS and tensor_core_ok(x, weight, gated, n_out):
         return linear_tensor_core(x, weight, out_float=out_float, gated=gated)
     if rows <= SMALL_ROWS:
         out_dtype = torch.float32 if (out_float or dt == 0) else x.dtype
@@ -173,10 +178,6 @@ def linear(x, weight, out_float=False, gated=False):
     return swiglu(y) if gated else y
 
 
-GEMM_MAX_TILES = 1 << 16
-_gemm_counters = {}
-
-
 def tensor_core_ok(x, weight, gated, n_out) -> bool:
     """Whether the tcgen05 product takes these operands: k a multiple of 8 (16-byte rows for TMA),
     16-byte aligned bases, gated widths in steps of 64."""
@@ -189,20 +190,29 @@ def tensor_core_ok(x, weight, gated, n_out) -> bool:
 
 
 def gemm_plan(rows: int, n_out: int, k_dim: int, gated: bool):
-    """``(bm, splits)``: activation rows per tile, and into how many CTAs the k range is cut so that
-    about two CTAs per SM stream the weights."""
+    """``(bm, splits, stages)``: activation rows per tile; how many CTAs (one cluster) share a tile's
+    k range; how deep the ring of shared-memory stages is.
+
+    With few rows the product is bound by streaming the weights: about two CTAs per SM should be
+    loading, each with some 100 KB in flight.  With many rows one CTA per SM holds a large tile."""
     bm = 16
     while bm < rows and bm < 256:
         bm *= 2
     tiles = (n_out // 64 if gated else -(-n_out // 128)) * -(-rows // bm)
     k_blocks = -(-k_dim // 64)
-    splits = max(1, min(k_blocks // 4, round(2 * 148 / tiles)))
-    if rows > 64:
-        splits = 1 if tiles >= 100 else max(1, min(k_blocks // 8, 148 // tiles))
-    return bm, splits
+    stage_bytes = 16384 + bm * 128
+    if rows <= 64:
+        # measured: four stages (three CTAs per SM) beat deeper rings; about 300 CTAs stream best
+        stages = 4
+        splits = max(1, min(8, k_blocks // 4, round(2 * 148 / tiles)))
+    else:
+        stages = max(3, min(6, (200 * 1024) // stage_bytes))
+        splits = 1 if tiles >= 100 else max(1, min(8, k_blocks // 8, 148 // tiles))
+    return bm, splits, stages
 
 
-def linear_tensor_core(x, weight, out_float=False, gated=False, bm=None, splits=None, status=None):
+def linear_tensor_core(x, weight, out_float=False, gated=False, bm=None, splits=None, stages=None,
+                       status=None):
     """The bfloat16 product on tcgen05 tensor cores (csrc/gemm_tcgen05.cu)."""
     _need(x, "x", torch.bfloat16, 2)
     _need(weight, "weight", torch.bfloat16, 2)
@@ -214,23 +224,14 @@ def linear_tensor_core(x, weight, out_float=False, gated=False, bm=None, splits=
     if not tensor_core_ok(x, weight, gated, n_out):
         raise KernelError(f"the tensor-core product needs k % 8 == 0, 16-byte aligned operands and gated "
                           f"widths in steps of 64; got k = {k_dim}, n = {n_out}")
-    plan_bm, plan_splits = gemm_plan(rows, n_out, k_dim, gated)
-    bm = bm or plan_bm
-    splits = splits or plan_splits
-    lib = build.load("gemm_tcgen05")
-    lib.sb_gemm_tcgen05_scratch.restype = ctypes.c_longlong
-    tiles = (n_out // 64 if gated else -(-n_out // 128)) * -(-rows // bm)
-    if tiles > GEMM_MAX_TILES:
-        raise KernelError(f"{tiles} output tiles exceed the {GEMM_MAX_TILES} the counters cover")
-    dev = x.device
-    if dev not in _gemm_counters:
-        _gemm_counters[dev] = torch.zeros((GEMM_MAX_TILES,), dtype=torch.int32, device=dev)
-    need = lib.sb_gemm_tcgen05_scratch(rows, n_out, splits, int(gated), bm)
-    scratch = torch.empty((need // 4,), dtype=torch.float32, device=dev) if need else None
-    out = torch.empty((rows, n_out), dtype=torch.float32 if out_float else torch.bfloat16, device=dev)
-    rc = lib.sb_gemm_tcgen05(_ptr(x), _ptr(weight), _ptr(out), rows, n_out, k_dim, bm, splits, int(gated),
-                             int(out_float), _ptr(scratch), _ptr(_gemm_counters[dev]), _ptr(status),
-                             _stream())
+    plan = gemm_plan(rows, n_out, k_dim, gated)
+    bm = bm or plan[0]
+    splits = splits or plan[1]
+    stages = stages or max(plan[2], -(-bm * 512 // (16384 + bm * 128)))
+    out = torch.empty((rows, n_out), dtype=torch.float32 if out_float else torch.bfloat16, device=x.device)
+    rc = build.load("gemm_tcgen05").sb_gemm_tcgen05(
+        _ptr(x), _ptr(weight), _ptr(out), rows, n_out, k_dim, bm, splits, stages, int(gated),
+        int(out_float), _ptr(status), _stream())
     if rc in (-3, -4):
         raise KernelError("the TMA descriptors for the tensor-core product could not be made "
                           f"(code {rc}); is the driver too old for cuTensorMapEncodeTiled?")

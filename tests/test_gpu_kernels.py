@@ -275,7 +275,8 @@ def test_attention_decode_split_over_keys(dtype, heads, kv_heads, d, window, spl
 
 @pytest.mark.parametrize("rows,n,k,gated,bm,splits", [
     (1, 128, 64, False, 16, 1), (8, 256, 512, False, 16, 2), (5, 300, 1000, False, None, None),
-    (16, 2560, 4096, False, None, None), (64, 1000, 2560, False, None, None), (3, 200, 264, False, 16, 9),
+    (16, 2560, 4096, False, None, None), (64, 1000, 2560, False, None, None), (3, 200, 264, False, 16, 5),
+    (64, 2560, 4096, False, 64, 8), (40, 384, 1024, True, 64, 4),
     (8, 1216, 2560, True, None, None), (33, 640, 2568, True, None, 3), (1, 64, 8, True, 16, 1),
     (200, 520, 1000, False, None, None), (600, 777, 264, False, 256, 1), (257, 130, 72, False, 128, 2)])
 def test_tensor_core_product(rows, n, k, gated, bm, splits):
