@@ -89,6 +89,136 @@ __global__ void qk_norm_rope_store_kernel(
   }
 }
 
+// The same for bfloat16 with 16-byte accesses: L = head_dim / 16 lanes share a head row, each holding
+// 8 elements of the low half and the 8 they pair with in the high half; a warp takes 32 / L rows.
+template <typename W, int L>
+__global__ void qk_norm_rope_store_vec_kernel(
+    const bf16* __restrict__ qkv, bf16* __restrict__ q_out, const W* __restrict__ q_gain,
+    const W* __restrict__ k_gain, const float* __restrict__ cos_table,
+    const float* __restrict__ sin_table, const int* __restrict__ tok_pos,
+    const int* __restrict__ tok_slot, const int* __restrict__ block_table, int table_stride,
+    bf16* __restrict__ k_store, bf16* __restrict__ v_store, long long n_rows, int heads, int kv_heads,
+    float eps, int heads_per_token, int row_stride) {
+  pdl_trigger();
+  pdl_wait();
+  constexpr int HALF = L * 8, D = 2 * HALF;
+  const long long item = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / L;
+  const int part = threadIdx.x % L;
+  const bool live = item < n_rows;
+  const long long it = live ? item : 0;
+  const int token = (int)(it / heads_per_token);
+  const int h = (int)(it - (long long)token * heads_per_token);
+  const bf16* src = qkv + (size_t)token * row_stride + (size_t)h * D + part * 8;
+  const int pos = tok_pos[token];
+  const bool is_q = h < heads;
+  const bool is_v = h >= heads + kv_heads;
+  bf16* dst;
+  if (is_q) {
+    dst = q_out + ((size_t)token * heads + h) * D;
+  } else {
+    const int kvh = is_v ? h - heads - kv_heads : h - heads;
+    const int page = block_table[(size_t)tok_slot[token] * table_stride + pos / SB_PAGE_TOKENS];
+    dst = (is_v ? v_store : k_store) + page_row(page, kvh, pos % SB_PAGE_TOKENS, kv_heads, D);
+  }
+  dst += part * 8;
+  uint4 raw_lo = *reinterpret_cast<const uint4*>(src);
+  uint4 raw_hi = *reinterpret_cast<const uint4*>(src + HALF);
+  if (is_v) {
+    if (live) {
+      *reinterpret_cast<uint4*>(dst) = raw_lo;
+      *reinterpret_cast<uint4*>(dst + HALF) = raw_hi;
+    }
+    // the shuffles below need every lane of a row's group; value rows fall in whole groups
+  }
+  float lo[8], hi[8];
+  {
+    const uint32_t wl[4] = {raw_lo.x, raw_lo.y, raw_lo.z, raw_lo.w}, wh[4] = {raw_hi.x, raw_hi.y, raw_hi.z, raw_hi.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      lo[2 * i] = __uint_as_float(wl[i] << 16); lo[2 * i + 1] = __uint_as_float(wl[i] & 0xffff0000u);
+      hi[2 * i] = __uint_as_float(wh[i] << 16); hi[2 * i + 1] = __uint_as_float(wh[i] & 0xffff0000u);
+    }
+  }
+  const W* gain = is_q ? q_gain : k_gain;
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) ss += lo[i] * lo[i] + hi[i] * hi[i];
+#pragma unroll
+  for (int o = L / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if (is_v || !live) return;
+  if (gain) {
+    const float inv = rsqrtf(ss / (float)D + eps);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      lo[i] = rnd<bf16>(rnd<bf16>(lo[i] * inv) * to_f<W>(gain[part * 8 + i]));
+      hi[i] = rnd<bf16>(rnd<bf16>(hi[i] * inv) * to_f<W>(gain[HALF + part * 8 + i]));
+    }
+  }
+  if (cos_table) {
+    const float* cp = cos_table + (size_t)pos * HALF + part * 8;
+    const float* sp = sin_table + (size_t)pos * HALF + part * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float c = rnd<bf16>(cp[i]), sn = rnd<bf16>(sp[i]);
+      const float a = rnd<bf16>(rnd<bf16>(lo[i] * c) + rnd<bf16>(-hi[i] * sn));
+      const float b = rnd<bf16>(rnd<bf16>(hi[i] * c) + rnd<bf16>(lo[i] * sn));
+      lo[i] = a;
+      hi[i] = b;
+    }
+  }
+  uint4 out_lo, out_hi;
+  {
+    uint32_t wl[4], wh[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 a = __floats2bfloat162_rn(lo[2 * i], lo[2 * i + 1]);
+      __nv_bfloat162 b = __floats2bfloat162_rn(hi[2 * i], hi[2 * i + 1]);
+      wl[i] = *reinterpret_cast<uint32_t*>(&a);
+      wh[i] = *reinterpret_cast<uint32_t*>(&b);
+    }
+    out_lo = make_uint4(wl[0], wl[1], wl[2], wl[3]);
+    out_hi = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+  }
+  *reinterpret_cast<uint4*>(dst) = out_lo;
+  *reinterpret_cast<uint4*>(dst + HALF) = out_hi;
+}
+
+template <typename W, int L>
+static int launch_vec(const void* qkv, void* q_out, const void* q_gain, const void* k_gain,
+                      const float* cos_table, const float* sin_table, const int* tok_pos,
+                      const int* tok_slot, const int* block_table, int table_stride, void* k_store,
+                      void* v_store, int n_tokens, int heads, int kv_heads, float eps, int write_cache,
+                      int row_stride, cudaStream_t s) {
+  const int per_token = write_cache ? heads + 2 * kv_heads : heads;
+  const long long rows = (long long)n_tokens * per_token;
+  if (rows == 0) return 0;
+  const int threads = 128;
+  const long long blocks = (rows * L + threads - 1) / threads;
+  return launch_dependent(qk_norm_rope_store_vec_kernel<W, L>, dim3((unsigned)blocks), dim3(threads), 0, s,
+      (const bf16*)qkv, (bf16*)q_out, (const W*)q_gain, (const W*)k_gain, cos_table, sin_table, tok_pos,
+      tok_slot, block_table, table_stride, (bf16*)k_store, (bf16*)v_store, rows, heads, kv_heads, eps,
+      per_token, row_stride);
+}
+
+template <typename W>
+static int launch_vec_by_dim(int head_dim, const void* qkv, void* q_out, const void* q_gain,
+                             const void* k_gain, const float* cos_table, const float* sin_table,
+                             const int* tok_pos, const int* tok_slot, const int* block_table,
+                             int table_stride, void* k_store, void* v_store, int n_tokens, int heads,
+                             int kv_heads, float eps, int write_cache, int row_stride, cudaStream_t s) {
+#define VARGS qkv, q_out, q_gain, k_gain, cos_table, sin_table, tok_pos, tok_slot, block_table, \
+              table_stride, k_store, v_store, n_tokens, heads, kv_heads, eps, write_cache, row_stride, s
+  switch (head_dim) {
+    case 16: return launch_vec<W, 1>(VARGS);
+    case 32: return launch_vec<W, 2>(VARGS);
+    case 64: return launch_vec<W, 4>(VARGS);
+    case 128: return launch_vec<W, 8>(VARGS);
+    case 256: return launch_vec<W, 16>(VARGS);
+    default: return -2;
+  }
+#undef VARGS
+}
+
 template <typename T, typename W>
 static int launch(const void* qkv, void* q_out, const void* q_gain, const void* k_gain,
                   const float* cos_table, const float* sin_table, const int* tok_pos,
@@ -122,6 +252,20 @@ int sb_qk_norm_rope_store(int dtype, int gain_dtype, const void* qkv, void* q_ou
 #define ARGS qkv, q_out, q_gain, k_gain, cos_table, sin_table, tok_pos, tok_slot, block_table, \
              table_stride, k_store, v_store, n_tokens, heads, kv_heads, head_dim, eps, write_cache, \
              row_stride, s
+  // bfloat16 with a power-of-two head size and 16-byte aligned rows takes the 16-byte kernel
+  const bool pow2 = head_dim >= 16 && head_dim <= 256 && (head_dim & (head_dim - 1)) == 0;
+  const bool aligned = row_stride % 8 == 0 && (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_store |
+                                                (uintptr_t)v_store) & 15) == 0;
+  if (dtype == 1 && pow2 && aligned) {
+    if (gain_dtype == 1)
+      return launch_vec_by_dim<bf16>(head_dim, qkv, q_out, q_gain, k_gain, cos_table, sin_table, tok_pos,
+                                     tok_slot, block_table, table_stride, k_store, v_store, n_tokens,
+                                     heads, kv_heads, eps, write_cache, row_stride, s);
+    if (gain_dtype == 0)
+      return launch_vec_by_dim<float>(head_dim, qkv, q_out, q_gain, k_gain, cos_table, sin_table, tok_pos,
+                                      tok_slot, block_table, table_stride, k_store, v_store, n_tokens,
+                                      heads, kv_heads, eps, write_cache, row_stride, s);
+  }
   if (dtype == 0 && gain_dtype == 0) return launch<float, float>(ARGS);
   if (dtype == 1 && gain_dtype == 1) return launch<bf16, bf16>(ARGS);
   if (dtype == 1 && gain_dtype == 0) return launch<bf16, float>(ARGS);

@@ -94,7 +94,9 @@ class ModelRunner:
                                    model.dtype, self.device, max_sequence_tokens)
         self.status = torch.zeros((1,), dtype=torch.int32, device=self.device)
         self.graphs = DecodeGraphs(self, max_sequences) if use_graphs else None
-        self.launches = 0
+        #: with False, every one-token step takes its tokens from the host (one small copy per step)
+        #: instead of from the token the device drew in the step before
+        self.self_feeding = True
 
     # ------------------------------------------------------------------ sequences
 
@@ -158,7 +160,7 @@ class ModelRunner:
         slots = tuple(e.slot for e in entries)
         for e in entries:
             cache.reserve(e.slot, cache.lengths[e.slot] + 1)
-        if graphs.fed != slots:
+        if graphs.fed != slots or not self.self_feeding:
             for e in entries:
                 if not 0 <= e.tokens[0] < self.model.spec.vocab_size:
                     raise ValueError(f"token id {e.tokens[0]} is outside the vocabulary")

@@ -60,9 +60,9 @@ def _need(t, name, dtype=None, ndim=None):
 launch_count = 0
 
 
-def _check(rc, what):
+def _check(rc, what, kernels=1):
     global launch_count
-    launch_count += 1
+    launch_count += kernels
     if rc != 0:
         if rc == -1:
             raise KernelError(f"{what}: this combination of dtypes has no kernel")
@@ -408,7 +408,7 @@ def attention_decode(q, k_store, v_store, block_table, row_slot, row_kv_len, hea
             block_table.shape[1], _ptr(row_slot), _ptr(row_kv_len), rows, heads, kv_heads, head_dim,
             ctypes.c_float(scale), int(window or 0), n_splits, _ptr(part_acc), _ptr(part_ml),
             _ptr(status), _stream())
-    _check(rc, "attention_decode")
+    _check(rc, "attention_decode", 2 if n_splits > 1 else 1)
     return out
 
 
@@ -436,5 +436,5 @@ def sample(logits, temperature=None, request_key=None, position=None, status=Non
         _ptr(request_key), _ptr(position), _ptr(out), _ptr(status),
         _ptr(feed[0] if feed else None), _ptr(feed[1] if feed else None),
         _ptr(feed[2] if feed else None), _ptr(cand_v), _ptr(cand_i), _stream())
-    _check(rc, "sample")
+    _check(rc, "sample", 2)
     return out

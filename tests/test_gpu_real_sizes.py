@@ -1,0 +1,88 @@
+"""One layer with the layer sizes of Qwen3-4B (hidden 2560, 32 query heads over 8 key/value heads of
+128, intermediate 9728) and an odd vocabulary: the kernels' real tile, split and stage choices, which
+the tiny configurations never reach, against the plain implementation."""
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from gpu_helpers import DTYPES, assert_close
+from tiny import random_prompt
+
+pytestmark = pytest.mark.gpu
+
+REAL = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=1, hidden_size=2560, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+    intermediate_size=9728, vocab_size=4099, rope_theta=5e6, rms_norm_eps=1e-6,
+    tie_word_embeddings=True, max_position_embeddings=4096, hidden_act="silu",
+)
+
+_made = {}
+
+
+def real_case(tmp_path_factory):
+    if not _made:
+        from starter_b200.config import config_from_dict
+        from starter_b200.weights import write_model_folder
+
+        folder = write_model_folder(str(tmp_path_factory.mktemp("real")), config_from_dict(REAL), 3,
+                                    torch.bfloat16)
+        cfg, w = plain.read_model_folder(folder)
+        _made["case"] = (folder, cfg, w)
+    return _made["case"]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_real_layer_sizes_whole_stepwise_and_batched(tmp_path_factory, dtype):
+    from starter_b200.engine import ModelRunner, StepEntry, load_model
+
+    folder, cfg, w = real_case(tmp_path_factory)
+    runner = ModelRunner(load_model(folder, dtype), max_tokens=64 * 40, max_sequences=16)
+    vocab = cfg["vocab_size"]
+    seqs = [random_prompt(n, vocab, 500 + n) for n in (300, 70, 9)]
+    want = [plain.plain_forward(cfg, w, s) for s in seqs]
+    # whole
+    slot = runner.open_sequence()
+    got = runner.step([StepEntry(slot, seqs[0], list(range(300)))])
+    runner.close_sequence(slot)
+    assert_close(got, want[0], dtype, "real sizes, 300 tokens whole")
+    # a batch of unequal prompts, then nine single-token steps of all three (rows = 3: the few-row
+    # kernels), the shortest leaving first
+    slots = [runner.open_sequence() for _ in seqs]
+    heads = [280, 61, 3]
+    out = runner.step([StepEntry(s, q[:h], [h - 1]) for s, q, h in zip(slots, seqs, heads)])
+    for i in range(3):
+        assert_close(out[i:i + 1], want[i][heads[i] - 1][None], dtype, f"real sizes, batched prompt {i}")
+    for step in range(9):
+        live = [i for i in range(3) if heads[i] + step < len(seqs[i])]
+        out = runner.step([StepEntry(slots[i], [seqs[i][heads[i] + step]], [0]) for i in live])
+        for row, i in enumerate(live):
+            assert_close(out[row:row + 1], want[i][heads[i] + step][None], dtype,
+                         f"real sizes, request {i} step {step}")
+    for s in slots:
+        runner.close_sequence(s)
+    runner.check_status()
+    runner.cache.check()
+
+
+def test_real_layer_sizes_graph_decode_of_a_full_batch(tmp_path_factory):
+    """Sixteen sequences decoded through the captured, self-feeding step: tokens equal to feeding the
+    same tokens step by step through the eager step function."""
+    from starter_b200 import Engine
+
+    folder, cfg, w = real_case(tmp_path_factory)
+    prompts = [random_prompt(5 + 7 * i, cfg["vocab_size"], 700 + i) for i in range(16)]
+    engine = Engine(folder, dtype="bfloat16", max_batch=16)
+    steps = list(engine.generate(prompts, 5))
+    engine.runner.graphs = None                       # the same loop without graphs
+    eager = list(engine.generate(prompts, 5))
+    margin = 3e-2 * 2
+    for i, prompt in enumerate(prompts[:4]):
+        seq = list(prompt)
+        for step in steps:
+            logits = plain.plain_forward(cfg, w, seq)[-1]
+            assert logits[step[i]].item() >= logits.max().item() - margin * max(1.0, logits.abs().max().item())
+            seq.append(step[i])
+    same = sum(a == b for s, e in zip(steps, eager) for a, b in zip(s, e))
+    assert same >= 0.9 * 16 * 5      # equal up to near-ties between bfloat16 logits
