@@ -109,7 +109,7 @@ def reference_arm():
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--steps", type=int, default=256)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--layers", type=int, default=QWEN3_4B["num_hidden_layers"],

@@ -148,6 +148,12 @@ __device__ __forceinline__ float ld_cluster(uint32_t addr) {
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
   return v;
 }
+__device__ __forceinline__ float4 ld_cluster4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+  return v;
+}
 __device__ __forceinline__ void cluster_sync() {
   asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
 }
@@ -301,33 +307,60 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     if (warp >= 2 && !*abort) {
       const uint32_t rank = args.splits > 1 ? cluster_rank() : 0;
       const int out_rows = args.gated ? 64 : TILE_N;
-      const int n_chunks = out_rows / 32 * rows_here;   // a chunk: 32 consecutive outputs of one row
+      const int per_row = out_rows / 4;                 // an item: four neighbouring outputs of a row
+      const int n_items = per_row * rows_here;
       const uint32_t base = smem_u32(part_sm);
       uint32_t remote[GEMM_MAX_SPLITS];
 #pragma unroll
       for (int s = 0; s < GEMM_MAX_SPLITS; ++s) remote[s] = s < args.splits && args.splits > 1 ? in_cta(base, s) : base;
-      for (int ch = rank + args.splits * (warp - 2); ch < n_chunks; ch += args.splits * 4) {
-        const int m = ch * 32 / out_rows;
-        const int orow = ch * 32 % out_rows + lane;
+      const bool vector_store = args.n_out % 4 == 0;
+      // blocks of 128 items go round the cluster; the loads of all parts of an item are in flight
+      // together and are added in split order
+      for (int item = rank * 128 + (threadIdx.x - 64); item < n_items; item += args.splits * 128) {
+        const int m = item / per_row;
+        const int orow = (item - m * per_row) * 4;
         const uint32_t at_g = (uint32_t)(m * TILE_N + orow) * 4;
-        float g = 0.f, u = 0.f;
+        float4 gv[GEMM_MAX_SPLITS], uv[GEMM_MAX_SPLITS];
 #pragma unroll
         for (int s = 0; s < GEMM_MAX_SPLITS; ++s) {
           if (s < args.splits) {
-            g += ld_cluster(remote[s] + at_g);
-            if (args.gated) u += ld_cluster(remote[s] + at_g + 64 * 4);
+            gv[s] = ld_cluster4(remote[s] + at_g);
+            if (args.gated) uv[s] = ld_cluster4(remote[s] + at_g + 64 * 4);
+          }
+        }
+        float g[4] = {0.f, 0.f, 0.f, 0.f}, u[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int s = 0; s < GEMM_MAX_SPLITS; ++s) {
+          if (s < args.splits) {
+            g[0] += gv[s].x; g[1] += gv[s].y; g[2] += gv[s].z; g[3] += gv[s].w;
+            if (args.gated) { u[0] += uv[s].x; u[1] += uv[s].y; u[2] += uv[s].z; u[3] += uv[s].w; }
+          }
+        }
+        if (args.gated) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float gr = rnd<bf16>(g[j]), ur = rnd<bf16>(u[j]);
+            g[j] = rnd<bf16>(gr / (1.f + __expf(-gr))) * ur;
           }
         }
         const int ncol = (args.gated ? tile * 64 : tile * TILE_N) + orow;
-        if (ncol < args.n_out) {
-          float y = g;
-          if (args.gated) {
-            const float gr = rnd<bf16>(g), ur = rnd<bf16>(u);
-            y = rnd<bf16>(gr / (1.f + __expf(-gr))) * ur;
+        const size_t at = (size_t)(m0 + m) * args.n_out + ncol;
+        if (vector_store && ncol + 3 < args.n_out) {
+          if (args.out_float) {
+            *reinterpret_cast<float4*>((float*)args.out + at) = make_float4(g[0], g[1], g[2], g[3]);
+          } else {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(g[0], g[1]), hi = __floats2bfloat162_rn(g[2], g[3]);
+            *reinterpret_cast<uint2*>((bf16*)args.out + at) =
+                make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
           }
-          const size_t at = (size_t)(m0 + m) * args.n_out + ncol;
-          if (args.out_float) ((float*)args.out)[at] = y;
-          else ((bf16*)args.out)[at] = __float2bfloat16_rn(y);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (ncol + j < args.n_out) {
+              if (args.out_float) ((float*)args.out)[at + j] = g[j];
+              else ((bf16*)args.out)[at + j] = __float2bfloat16_rn(g[j]);
+            }
+          }
         }
       }
     }
