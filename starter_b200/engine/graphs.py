@@ -39,6 +39,7 @@ class DecodeGraphs:
         self.logits = {}
         self.kernels_per_replay = {}  # this library's kernels inside each graph
         self.fed = None  # the slots whose next inputs the device already holds
+        self.kv_hint = 0  # longest sequence of the batch when its graph is captured (sizes the splits)
 
     def _field(self, name, batch):
         return self.meta[self.fields.index(name), :batch]
@@ -51,7 +52,8 @@ class DecodeGraphs:
             seq_q_start=self.rows[:batch], seq_q_len=self.ones[:batch],
             seq_kv_len=self._field("kv_len", batch), want_rows=self.rows[:batch],
             tile_seq=self.rows[:batch], tile_first=self.zeros[:batch],
-            max_q_len=1, max_kv_len=0, cache=self.runner.cache, status=self.runner.status, host=None)
+            max_q_len=1, max_kv_len=self.kv_hint, cache=self.runner.cache, status=self.runner.status,
+            host=None)
 
     def _body(self, batch: int):
         model = self.runner.model
@@ -91,6 +93,7 @@ class DecodeGraphs:
     def load(self, slots, tokens, positions, temperatures, keys) -> None:
         """Put a batch's rows on the device (one copy)."""
         batch = len(slots)
+        self.kv_hint = max(positions) + 1
         host = np.zeros((len(self.fields), batch), dtype=np.int32)
         host[0] = tokens
         host[1] = positions

@@ -362,15 +362,19 @@ def decode_attention_takes(head_dim: int, dtype) -> bool:
     return head_dim in DECODE_HEAD_DIMS and head_dim * dtype.itemsize <= 512
 
 
-def decode_splits(rows: int, kv_heads: int, groups: int, group_rows: int = 4) -> int:
+def decode_splits(rows: int, kv_heads: int, groups: int, group_rows: int = 4, kv_hint: int = 0) -> int:
     """How many parts to cut each row's keys into: as many as keep all blocks resident at once
-    (two per SM), so that no block waits for a second wave."""
+    (two per SM), so that no block waits for a second wave, but at least three pages per part when
+    the longest sequence is known (``kv_hint`` tokens)."""
     blocks = rows * kv_heads * (-(-groups // group_rows))
-    return max(1, min(32, (2 * 148) // blocks))
+    splits = max(1, min(32, (2 * 148) // blocks))
+    if kv_hint > 0:
+        splits = max(1, min(splits, -(-kv_hint // (3 * PAGE_TOKENS))))
+    return splits
 
 
 def attention_decode(q, k_store, v_store, block_table, row_slot, row_kv_len, heads, kv_heads, head_dim,
-                     scale, window=None, n_splits=None, status=None):
+                     scale, window=None, n_splits=None, status=None, kv_hint=0):
     """One query per row (the newest token of its sequence) over that sequence's cached keys.
 
     ``row_kv_len[r]`` is the sequence's length with the query's own key already filed; the lengths
@@ -393,7 +397,7 @@ def attention_decode(q, k_store, v_store, block_table, row_slot, row_kv_len, hea
     _need(row_kv_len, "row_kv_len", torch.int32, 1)
     tensor_cores = q.dtype == torch.bfloat16 and head_dim in PREFILL_HEAD_DIMS
     if n_splits is None:
-        n_splits = decode_splits(rows, kv_heads, heads // kv_heads, 16 if tensor_cores else 4)
+        n_splits = decode_splits(rows, kv_heads, heads // kv_heads, 16 if tensor_cores else 4, kv_hint)
     out = torch.empty_like(q)
     part_acc = part_ml = None
     if n_splits > 1:

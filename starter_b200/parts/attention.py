@@ -76,7 +76,7 @@ class GroupedQueryAttention(Part):
         if ctx.max_q_len == 1 and ops.decode_attention_takes(s.head_dim, q.dtype):
             a = ops.attention_decode(q, keys, values, cache.block_table, ctx.seq_slot, ctx.seq_kv_len,
                                      s.num_heads, s.num_kv_heads, s.head_dim, s.scale, s.window,
-                                     status=ctx.status)
+                                     status=ctx.status, kv_hint=ctx.max_kv_len)
         elif q.dtype == torch.bfloat16 and s.head_dim in ops.PREFILL_HEAD_DIMS:
             a = ops.attention_prefill(q, keys, values, cache.block_table, ctx.seq_slot, ctx.seq_q_start,
                                       ctx.seq_q_len, ctx.seq_kv_len, ctx.tile_seq, ctx.tile_first,
