@@ -44,18 +44,22 @@ class Engine:
             self._build_runner(max_tokens)
         return self
 
-    def _build_runner(self, max_tokens: int) -> None:
+    def _build_runner(self, max_tokens: int, longest: int | None = None) -> None:
         self.runner = None
         torch.cuda.empty_cache()
-        self.runner = ModelRunner(self.model, max_tokens, max_sequences=max(self.max_batch, 1))
+        self.runner = ModelRunner(self.model, max_tokens, max_sequences=max(self.max_batch, 1),
+                                  max_sequence_tokens=longest)
         self.sampler = Sampler(self.model.device, self.runner.status)
 
     def _ensure_room(self, requests, batch: int) -> GenerationLoop:
         pages = sorted((pages_held(r) for r in requests), reverse=True)
         need = sum(pages[:batch]) * 64
-        if self.runner is None or (self._fixed_tokens is None and need > self.runner.cache.num_pages * 64):
+        cache = self.runner.cache if self.runner is not None else None
+        small = cache is not None and self._fixed_tokens is None and (
+            need > cache.num_pages * 64 or pages[0] > cache.max_pages_per_sequence)
+        if cache is None or small:
             print(f"[engine] building the cache for {need} tokens", flush=True)
-            self._build_runner(max(need, 64))
+            self._build_runner(max(need, 64), None if self._fixed_tokens else pages[0] * 64)
         return GenerationLoop(self.runner, self.sampler, batch, self.runner.cache.num_pages)
 
     # ------------------------------------------------------------------ the reference's call

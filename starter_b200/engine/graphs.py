@@ -66,7 +66,17 @@ class DecodeGraphs:
                          self._field("kv_len", batch)))
         return logits
 
+    def drop(self) -> None:
+        """Forget every captured graph (device tables they read were reallocated)."""
+        self.graphs.clear()
+        self.logits.clear()
+        self.kernels_per_replay.clear()
+
     def _capture(self, batch: int) -> None:
+        # tables that grow with the sequence are sized for the longest sequence the cache can hold
+        # before anything is captured, so that a long generation does not move them mid-way
+        cache = self.runner.cache
+        self.runner.model.prepare(cache.max_pages_per_sequence * 64)
         saved = self.meta.clone()
         # warm up on a side stream (compiles kernels, sizes library workspaces), then capture;
         # both run the real step, so the fields are restored afterwards and the cache rows the

@@ -117,10 +117,13 @@ class DecoderModel:
 
     # ------------------------------------------------------------------ compute
 
-    def prepare(self, max_position: int) -> None:
-        """Host-side growth (position tables) that must not happen in the middle of a step."""
+    def prepare(self, max_position: int) -> bool:
+        """Host-side growth (position tables) that must not happen in the middle of a step.  True if
+        any device table moved: graphs captured before then hold stale addresses."""
+        moved = False
         for block in self.blocks:
-            block.mixer.prepare(max_position)
+            moved = bool(block.mixer.prepare(max_position)) or moved
+        return moved
 
     def hidden(self, ctx):
         """Run the layers; returns ``(residual, pending)`` with the last sum still open."""

@@ -110,6 +110,11 @@ class ModelRunner:
         """Set pages aside so that ``slot`` can grow to ``tokens`` tokens without asking again."""
         self.cache.reserve(slot, tokens)
 
+    def prepare(self, max_position: int) -> None:
+        """Grow what depends on the longest sequence; captured graphs that read moved tables go."""
+        if self.model.prepare(max_position) and self.graphs is not None:
+            self.graphs.drop()
+
     # ------------------------------------------------------------------ the step
 
     def make_context(self, entries) -> StepContext:
@@ -123,7 +128,7 @@ class ModelRunner:
         cache.sync_table()
         dev = upload(arrays, self.device)
         max_kv = int(arrays["seq_kv_len"].max())
-        self.model.prepare(max_kv)
+        self.prepare(max_kv)
         return StepContext(
             n_tokens=int(arrays["tokens"].size), n_seqs=len(entries),
             tokens=dev["tokens"], tok_pos=dev["tok_pos"], tok_slot=dev["tok_slot"],
@@ -169,7 +174,7 @@ class ModelRunner:
         for s in slots:
             cache.advance(s, 1)
         cache.sync_table()
-        self.model.prepare(max(cache.lengths[s] for s in slots))
+        self.prepare(max(cache.lengths[s] for s in slots))
         return graphs.replay(len(slots))
 
     def check_status(self) -> None:

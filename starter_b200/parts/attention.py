@@ -57,9 +57,11 @@ class GroupedQueryAttention(Part):
         if self.spec.qk_norm:
             self.q_norm, self.k_norm = params["q_norm"], params["k_norm"]
 
-    def prepare(self, max_position: int) -> None:
+    def prepare(self, max_position: int) -> bool:
+        """Host-side growth before a step; True if device tables were reallocated."""
         if self.position is not None:
-            self.position.ensure(max_position + 1)
+            return bool(self.position.ensure(max_position + 1))
+        return False
 
     def __call__(self, x, ctx, entry, writes_cache=True):
         s = self.spec

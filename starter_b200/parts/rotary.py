@@ -33,10 +33,11 @@ class RotaryTable(Part):
         pos = torch.arange(length, dtype=torch.int64).float()
         return torch.outer(pos, inv_freq)
 
-    def ensure(self, length: int) -> None:
-        """Make the tables cover positions ``[0, length)``."""
+    def ensure(self, length: int) -> bool:
+        """Make the tables cover positions ``[0, length)``; True if they moved (captured graphs that
+        read the old tables must then be dropped)."""
         if length <= self.length:
-            return
+            return False
         size = max(self.MIN_POSITIONS, self.length)
         while size < length:
             size *= 2
@@ -44,3 +45,4 @@ class RotaryTable(Part):
         self.cos = freqs.cos().contiguous().to(self.device)
         self.sin = freqs.sin().contiguous().to(self.device)
         self.length = size
+        return True
