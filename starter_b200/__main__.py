@@ -7,8 +7,10 @@ README.md:54-66).
   generate      --model-path DIR --input-ids "1,2,3;4,5" --max-new-tokens N
                 [--temperature T] [--seed S] [--stop-token-ids 7,9] [--dtype bfloat16|float32]
                 [--max-batch B]                 prints one JSON line per prompt
+                instead of --input-ids: --prompt-lens 5,3 [--prompt-seed P] draws uniform random ids
   random-model  --config CONFIG.json --seed S --out DIR [--dtype float32|bfloat16]
                                                 writes config.json and model.safetensors
+  replay        --model DIR --dtype D --out DIR --max-tokens N      (bin/trace_run; steps on stdin)
 """
 
 from __future__ import annotations
@@ -34,8 +36,11 @@ def main(argv=None) -> int:
 
     gen = sub.add_parser("generate", help="generate from prompts given as token ids")
     gen.add_argument("--model-path", required=True, help="folder with config.json and safetensors")
-    gen.add_argument("--input-ids", required=True,
+    gen.add_argument("--input-ids", default=None,
                      help='token ids, prompts separated by ";": "1,2,3;4,5"; or @FILE with a JSON list of lists')
+    gen.add_argument("--prompt-lens", default=None,
+                     help="instead of --input-ids: comma-separated lengths of uniform random prompts")
+    gen.add_argument("--prompt-seed", type=int, default=0, help="seed of the random prompts")
     gen.add_argument("--max-new-tokens", type=int, required=True)
     gen.add_argument("--temperature", type=float, default=0.0, help="0 = greedy (default)")
     gen.add_argument("--seed", type=int, default=0, help="sampling seed")
@@ -49,6 +54,12 @@ def main(argv=None) -> int:
     rnd.add_argument("--out", required=True)
     rnd.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
 
+    sub.add_parser("replay", help="trace replay (same as bin/trace_run)", add_help=False)
+
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if argv and argv[0] == "replay":
+        from .replay import main as replay_main
+        return replay_main(argv[1:])
     args = parser.parse_args(argv)
     if args.command == "random-model":
         from .config import config_from_dict
@@ -63,7 +74,18 @@ def main(argv=None) -> int:
 
     from .engine.entry import Engine
 
-    if args.input_ids.startswith("@"):
+    if (args.input_ids is None) == (args.prompt_lens is None):
+        parser.error("give exactly one of --input-ids and --prompt-lens")
+    if args.prompt_lens is not None:
+        import torch
+
+        from .config import load_config
+
+        vocab = load_config(args.model_path).vocab_size
+        draw = torch.Generator().manual_seed(args.prompt_seed)
+        prompts = [torch.randint(0, vocab, (int(n),), generator=draw).tolist()
+                   for n in args.prompt_lens.split(",") if n.strip()]
+    elif args.input_ids.startswith("@"):
         with open(args.input_ids[1:]) as handle:
             prompts = json.load(handle)
     else:

@@ -97,3 +97,26 @@ def test_replay_whole_stepwise_and_batched(tmp_path_factory, tmp_path, name, dty
         assert rows.shape[0] == len(places)
         for row, (r, place) in zip(rows, places):
             assert_close(row[None], want[r][place][None], dtype, f"batched {r} place {place}")
+
+
+def test_command_line_generates_what_the_plain_implementation_generates(tmp_path_factory):
+    folder, cfg, w = model_case(tmp_path_factory, "A")
+    prompts = [random_prompt(5, cfg["vocab_size"], 1), random_prompt(3, cfg["vocab_size"], 2)]
+    text = ";".join(",".join(str(t) for t in p) for p in prompts)
+    out = subprocess.run([sys.executable, "-m", "starter_b200", "generate", "--model-path", folder,
+                          "--input-ids", text, "--max-new-tokens", "4", "--dtype", "float32"],
+                         cwd=ROOT, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    lines = [json.loads(l) for l in out.stdout.splitlines() if l.startswith("{")]
+    assert [l["tokens"] for l in lines] == [plain.plain_generate(cfg, w, p, 4) for p in prompts]
+    assert all(l["finish_reason"] == "length" for l in lines)
+    # random prompts by length, a temperature, a stop token
+    out = subprocess.run([sys.executable, "-m", "starter_b200", "generate", "--model-path", folder,
+                          "--prompt-lens", "7,2", "--prompt-seed", "9", "--max-new-tokens", "5", "--dtype",
+                          "float32", "--temperature", "0.9", "--seed", "4"],
+                         cwd=ROOT, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    lines = [json.loads(l) for l in out.stdout.splitlines() if l.startswith("{")]
+    draw = torch.Generator().manual_seed(9)
+    drawn = [torch.randint(0, cfg["vocab_size"], (n,), generator=draw).tolist() for n in (7, 2)]
+    assert [l["tokens"] for l in lines] == [plain.plain_generate(cfg, w, p, 5, 0.9, 4, i) for i, p in enumerate(drawn)]
