@@ -179,3 +179,136 @@ def test_a_toy_mixer_with_state_registers_builds_and_steps(dtype):
     ctx = runner.make_context([StepEntry(s, b, [])])
     got = model.blocks[0].mixer(model.blocks[0].norm1(model.embed[torch.tensor(b, device="cuda")].contiguous()), ctx, 0, True)
     assert_close(got, want, dtype, "toy mixer alone")
+
+
+# ----------------------------------------------------------------------------- more toy parts
+
+@dataclass(frozen=True)
+class RoutedFeedForwardSpec:
+    hidden_size: int
+    intermediate_size: int
+    num_experts: int
+    kind: str = "toy_routed"
+
+
+class RoutedFeedForward:
+    """Top-1 routing over small gated experts; router logits and the choice in float32."""
+
+    def __init__(self, spec, dtype):
+        self.spec, self.dtype = spec, dtype
+
+    def param_specs(self):
+        from starter_b200.parts import ParamSpec
+        s = self.spec
+        out = {"router": ParamSpec((s.num_experts, s.hidden_size))}
+        for e in range(s.num_experts):
+            out[f"gate_up{e}"] = ParamSpec((2 * s.intermediate_size, s.hidden_size))
+            out[f"down{e}"] = ParamSpec((s.hidden_size, s.intermediate_size))
+        return out
+
+    def set_params(self, params):
+        self.p = params
+
+    def weight_bytes(self):
+        return sum(t.numel() * t.element_size() for t in self.p.values())
+
+    def __call__(self, x, ctx=None):
+        from starter_b200 import ops
+        choice = (x.float() @ self.p["router"].float().t()).argmax(-1)
+        out = torch.zeros_like(x)
+        for e in range(self.spec.num_experts):
+            rows = (choice == e).nonzero().flatten()
+            if rows.numel():
+                xe = x[rows].contiguous()
+                out[rows] = ops.linear(ops.linear(xe, self.p[f"gate_up{e}"], gated=True), self.p[f"down{e}"])
+        return out
+
+
+@dataclass(frozen=True)
+class ScaledRopeSpec:
+    head_dim: int
+    theta: float
+    factor: float
+    kind: str = "toy_scaled_rope"
+
+
+def scaled_rope_class():
+    from starter_b200.parts import RotaryTable
+
+    class ScaledRope(RotaryTable):
+        """Rotary positions with every position divided by a factor (position interpolation)."""
+
+        def ensure(self, length):
+            if length <= self.length:
+                return False
+            size = max(64, self.length)
+            while size < length:
+                size *= 2
+            freqs = self.angles(self.spec.theta, self.spec.head_dim, size) / self.spec.factor
+            self.cos = freqs.cos().contiguous().to(self.device)
+            self.sin = freqs.sin().contiguous().to(self.device)
+            self.length = size
+            return True
+
+    return ScaledRope
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_routed_feed_forward_and_another_position_encoding_plug_in(dtype):
+    """A model whose layers differ: attention with scaled rotary positions + routed experts, then the
+    library's attention with its own rotary positions + the dense feed-forward.  Built from specs,
+    stepped whole and in pieces, and the first layer checked against plain torch."""
+    from starter_b200.config import (AttentionSpec, GatedFeedForwardSpec, LayerSpec, ModelSpec, NormSpec,
+                                     RopeSpec, default_schedule)
+    from starter_b200.engine import DecoderModel, ModelRunner, StepEntry
+    from starter_b200.parts import register
+    from starter_b200.weights import random_checkpoint
+
+    register("feed_forward", "toy_routed", RoutedFeedForward)
+    register("position", "toy_scaled_rope", scaled_rope_class())
+    hidden, vocab = 64, 97
+    norm = NormSpec(hidden, 1e-6)
+
+    def attn(position):
+        return AttentionSpec(hidden, 4, 2, 16, 0.25, True, 1e-6, position)
+
+    def names(i, ff_names):
+        out = {"norm1.weight": f"l{i}.n1", "norm2.weight": f"l{i}.n2"}
+        out.update({f"mixer.{k}": f"l{i}.attn.{k}" for k in ("q", "k", "v", "o", "q_norm", "k_norm")})
+        out.update({f"feed_forward.{k}": f"l{i}.ff.{k}" for k in ff_names})
+        return out
+
+    routed = RoutedFeedForwardSpec(hidden, 48, 3)
+    routed_names = ["router"] + [f"{k}{e}" for e in range(3) for k in ("gate_up", "down")]
+    layers = (
+        LayerSpec(attn(ScaledRopeSpec(16, 1e4, 4.0)), routed, norm, norm, names(0, routed_names)),
+        LayerSpec(attn(RopeSpec(16, 1e4)), GatedFeedForwardSpec(hidden, 80), norm, norm, names(1, ["gate", "up", "down"])),
+    )
+    spec = ModelSpec("Toy2", vocab, hidden, layers, default_schedule(2), norm, False, "embed", "final", "head")
+    model = DecoderModel(spec, DT[dtype], "cuda")
+    tensors = random_checkpoint(model.expected_tensors(), 5, DT[dtype], "cuda")
+    model.load_tensors(tensors)
+    assert len(model.positions) == 2                     # two position parts, not shared
+    runner = ModelRunner(model, max_tokens=64 * 4, max_sequences=4)
+    seq = random_prompt(90, vocab, 3)
+    s = runner.open_sequence()
+    whole = runner.step([StepEntry(s, seq, list(range(90)))])
+    runner.close_sequence(s)
+    s = runner.open_sequence()
+    parts = [runner.step([StepEntry(s, seq[:70], list(range(70)))])]
+    parts += [runner.step([StepEntry(s, [t], [0])]) for t in seq[70:]]
+    assert_close(torch.cat(parts), whole, dtype, "toy model 2, cut in steps")
+    # the scaled positions really are used: the first layer's mixer equals the plain mixer run with
+    # tables of positions / 4
+    w = {k: v.cpu() for k, v in tensors.items()}
+    x = torch.randn(12, hidden, generator=torch.Generator().manual_seed(1)).to(DT[dtype])
+    cos, sin = plain.plain_rope_tables(1e4, 16, 12, torch.float32)
+    freqs = torch.outer(torch.arange(12).float(), 1.0 / (1e4 ** (torch.arange(0, 16, 2).float() / 16))) / 4.0
+    emb = torch.cat((freqs, freqs), -1)
+    cfg = dict(num_attention_heads=4, num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-6, hidden_size=hidden)
+    renamed = {f"model.layers.0.self_attn.{k}_proj.weight": w[f"l0.attn.{k}"] for k in "qkvo"}
+    renamed.update({f"model.layers.0.self_attn.{k}_norm.weight": w[f"l0.attn.{k}_norm"] for k in "qk"})
+    want = plain.plain_mixer(x, renamed, "model.layers.0.", cfg, emb.cos().to(DT[dtype]), emb.sin().to(DT[dtype]), None)
+    slot, ctx = one_sequence_context(runner, 12)
+    got = model.blocks[0].mixer(x.cuda(), ctx, 0, True)
+    assert_close(got, want, dtype, "mixer with scaled rotary positions")
