@@ -1,0 +1,535 @@
+// Causal grouped-query attention for prompts on the fifth-generation tensor cores (bfloat16).
+//
+// A CTA takes 128 consecutive query tokens of one sequence and one query head.  Both products run as
+// tcgen05.mma with the accumulators in tensor memory:
+//     S   = Q K^T     M = 128 queries, N = 128 keys,     K = head_dim   (K and Q K-major)
+//     O_j = P V       M = 128 queries, N = head_dim,     K = 128 keys   (V as it lies in the cache:
+//                                                                        keys x head_dim, "MN-major")
+// TMA brings Q once and, per step of 128 keys (two cache pages), K and V into a two-stage ring with
+// the 128-byte swizzle the tensor core reads.  Four warps own the 128 rows (thread = query row =
+// TMEM lane): they read S with tcgen05.ld, do the online softmax in float without any shuffle
+// (engine/kernels/fused.py:288-312), write P rounded to bfloat16 (fused.py:699-701) into shared
+// memory as the next A operand, and fold each O_j into the running output held in registers.
+// One thread issues all MMAs; while the softmax warps fold O_j, S of the next step is already being
+// computed.  Keys are read from the cache like in every other attention kernel of this library, so a
+// chunk that continues a sequence needs nothing special: a query at absolute position p sees keys
+// j <= p (engine/engine.py:781-787) and, with a window w, j > p - w.
+//
+// Every wait on an mbarrier gives up after WAIT_LIMIT_NS, raises bit 16 of *status and lets the CTA
+// drain, free its tensor memory and return.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define TC_BQ 128
+#define TC_BK 128
+#define TC_THREADS 320
+#define TC_RING 3
+#define WAIT_LIMIT_NS 2000000000ull
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint64_t now_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
+#pragma unroll 1
+  for (int spin = 0; spin < 2048; ++spin)
+    if (mbar_try(bar, parity)) return true;
+  const uint64_t start = now_ns();
+#pragma unroll 1
+  for (uint32_t spin = 0;; ++spin) {
+    if (mbar_try(bar, parity)) return true;
+    if ((spin & 63) == 0) {
+      if (*abort) return false;
+      if (now_ns() - start > WAIT_LIMIT_NS) { *abort = 1; return false; }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* holder, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(holder)), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_free(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// 32 consecutive float columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, float* v) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// 64 consecutive 32-bit columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_load64(uint32_t taddr, float* v) {
+  uint32_t r[64];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
+      "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
+      "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]),
+        "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]),
+        "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]),
+        "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]),
+        "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+      : "r"(taddr)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+}
+// 32 columns back into this thread's TMEM lane
+__device__ __forceinline__ void tmem_store32(uint32_t taddr, const float* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])),
+        "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])),
+        "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+        "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])),
+        "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])),
+        "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
+        "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])),
+        "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Operand tile with rows of 128 bytes and 128-byte swizzle, 8-row groups 1024 bytes apart.  For a
+// K-major operand the rows are M/N and `lbo` is unused; for an MN-major operand the rows are k and
+// `lbo` is the distance between 64-element chunks along M/N.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// kind::f16, float accumulator, bfloat16 operands, A K-major, M = 128; B K-major or MN-major.
+__device__ __forceinline__ uint32_t instr_desc(int n, int b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(TC_BQ >> 4) << 24);
+}
+
+template <int D>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
+                            const int* __restrict__ block_table, int table_stride,
+                            const int* __restrict__ seq_slot, const int* __restrict__ seq_q_start,
+                            const int* __restrict__ seq_q_len, const int* __restrict__ seq_kv_len,
+                            const int* __restrict__ tile_seq, const int* __restrict__ tile_first,
+                            int heads, int kv_heads, float scale_log2, int window, int* status) {
+  constexpr int DC = D / 64;                        // 64-element (128-byte) chunks of the head
+  constexpr int SUB = 128 * 128;                    // bytes of a [128 rows x 128 bytes] sub-tile
+  constexpr int Q_BYTES = DC * SUB;                 // one tile of 128 queries
+  constexpr int KV_BYTES = DC * SUB;                // keys (or values) of 128 tokens
+  constexpr int P_BYTES = 2 * SUB;                  // [128 queries x 128 keys] bfloat16
+  constexpr uint32_t TMEM_COLS = 512;               // S of both tiles: 2 x 128; O of both tiles: 2 x 128
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* q_sm = smem;                             // 2 tiles
+  uint8_t* p_sm = q_sm + 2 * Q_BYTES;               // 2 tiles
+  uint8_t* ring = p_sm + 2 * P_BYTES;               // TC_RING buffers: K0 V0 K1 V1 ... in turn
+  __shared__ uint64_t q_full, full[TC_RING], empty[TC_RING], s_ready[2], p_ready[2], o_ready[2];
+  __shared__ uint32_t tmem_holder;
+  __shared__ int abort_flag;
+
+  const int tile = blockIdx.y, head = blockIdx.x;   // heads run fastest: the work list's order holds
+  const int q_first = tile_first[tile];
+  if (q_first & 255) return;                         // the work list is in tiles of 64: four make one block
+  const int seq = tile_seq[tile];
+  const int q_len = seq_q_len[seq], kv_len = seq_kv_len[seq];
+  const int rows_valid = min(2 * TC_BQ, q_len - q_first);
+  const int pos0 = kv_len - q_len + q_first;
+  const int kvh = head / (heads / kv_heads);
+  const int* pages = block_table + (size_t)seq_slot[seq] * table_stride;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const int hi = pos0 + rows_valid - 1;
+  int lo = 0;
+  if (window > 0 && pos0 - window + 1 > 0) lo = pos0 - window + 1;
+  const int page_lo = lo / SB_PAGE_TOKENS, page_hi = hi / SB_PAGE_TOKENS;
+  // steps of two pages (128 keys) that each tile of 128 queries needs, counted from page_lo
+  int n_tile[2];
+  n_tile[0] = ((pos0 + min(rows_valid, TC_BQ) - 1) / SB_PAGE_TOKENS - page_lo) / 2 + 1;
+  n_tile[1] = rows_valid > TC_BQ ? (page_hi - page_lo) / 2 + 1 : 0;
+  const int n_steps = max(n_tile[0], n_tile[1]);
+
+  if (threadIdx.x == 0) {
+    mbar_init(&q_full, 1);
+    for (int s = 0; s < TC_RING; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&s_ready[t], 1);
+      mbar_init(&p_ready[t], 4);      // one arrival per softmax warp
+      mbar_init(&o_ready[t], 1);
+    }
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  pdl_trigger();
+  if (warp == 9) tmem_alloc(&tmem_holder, TMEM_COLS);
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_holder;
+  volatile int* abort = &abort_flag;
+
+  if (warp == 8) {
+    // ---------------- producer: Q, then K0 V0 K1 V1 ... through the ring
+    if (lane == 0) {
+      pdl_wait();
+      const int q_row0 = seq_q_start[seq] + q_first;
+      const int q_tiles = n_tile[1] ? 2 : 1;
+      mbar_expect_tx(&q_full, q_tiles * Q_BYTES);
+      for (int t = 0; t < q_tiles; ++t)
+        for (int c = 0; c < DC; ++c)
+          tma_load_2d(q_sm + t * Q_BYTES + c * SUB, &map_q, &q_full, head * D + c * 64, q_row0 + t * TC_BQ);
+      int issued = 0;
+      for (int j = 0; j < 2 * n_steps; ++j) {
+        const int b = j % TC_RING, use = j / TC_RING;
+        if (use > 0 && !mbar_wait(&empty[b], (use - 1) & 1, abort)) break;
+        mbar_expect_tx(&full[b], KV_BYTES);
+        const CUtensorMap* map = (j & 1) ? &map_v : &map_k;
+        for (int half = 0; half < 2; ++half) {
+          const int page = pages[min(page_lo + 2 * (j >> 1) + half, page_hi)];
+          const int row = (page * kv_heads + kvh) * SB_PAGE_TOKENS;
+          for (int c = 0; c < DC; ++c)
+            tma_load_2d(ring + b * KV_BYTES + c * SUB + half * 8192, map, &full[b], c * 64, row);
+        }
+        issued = j + 1;
+      }
+      if (*abort) {                                    // let the copies in flight land before the block ends
+        for (int j = max(issued - TC_RING, 0); j < issued; ++j) {
+          const uint64_t start = now_ns();
+          while (!mbar_try(&full[j % TC_RING], (j / TC_RING) & 1) && now_ns() - start < WAIT_LIMIT_NS) {}
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // ---------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_s = instr_desc(TC_BK, 0), idesc_o = instr_desc(D, 1);
+      // S_t = Q_t K^T: k runs over the head in steps of 16 (32 bytes inside a 128-byte chunk)
+      auto issue_s = [&](int t, int buf) {
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k >> 2) * SUB + (k & 3) * 32;
+          umma_bf16(tmem_base + t * TC_BK, smem_desc(smem_u32(q_sm + t * Q_BYTES) + off, 16),
+                    smem_desc(smem_u32(ring + buf * KV_BYTES) + off, 16), idesc_s, k > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_ready[t]);
+      };
+      // O_t (+)= P_t V: k runs over the 128 keys in steps of 16; P K-major (two 64-key chunks); V's
+      // rows are keys (16 keys = 2048 bytes), its 64-wide chunks of the head are SUB bytes apart
+      auto issue_pv = [&](int t, int buf, bool first) {
+#pragma unroll
+        for (int k = 0; k < TC_BK / 16; ++k) {
+          const uint32_t a_off = (k >> 2) * SUB + (k & 3) * 32;
+          umma_bf16(tmem_base + 2 * TC_BK + t * 128, smem_desc(smem_u32(p_sm + t * P_BYTES) + a_off, 16),
+                    smem_desc(smem_u32(ring + buf * KV_BYTES) + k * 2048, SUB), idesc_o,
+                    (first && k == 0) ? 0u : 1u);
+        }
+        umma_commit(&o_ready[t]);
+      };
+      bool ok = mbar_wait(&q_full, 0, abort) && mbar_wait(&full[0], 0, abort);
+      if (ok) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        for (int t = 0; t < 2; ++t)
+          if (n_tile[t] > 0) issue_s(t, 0);
+        umma_commit(&empty[0]);
+      }
+      for (int i = 0; i < n_steps && ok; ++i) {
+        const int jv = 2 * i + 1, jk = 2 * i + 2;
+        const bool more = i + 1 < n_steps;
+        ok = mbar_wait(&full[jv % TC_RING], (jv / TC_RING) & 1, abort);
+        if (ok && more) ok = mbar_wait(&full[jk % TC_RING], (jk / TC_RING) & 1, abort);
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (i >= n_tile[t]) continue;
+          ok = mbar_wait(&p_ready[t], i & 1, abort);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          issue_pv(t, jv % TC_RING, i == 0);
+          if (i + 1 < n_tile[t]) issue_s(t, jk % TC_RING);
+        }
+        if (!ok) break;
+        umma_commit(&empty[jv % TC_RING]);
+        if (more) umma_commit(&empty[jk % TC_RING]);
+      }
+    }
+  } else if (warp < 8) {
+    // ---------------- softmax and output: warps 0-3 own tile 0, warps 4-7 tile 1; thread = query
+    // row = TMEM lane.  The running output stays in tensor memory; it is rescaled only when a row's
+    // maximum has grown by more than 2^8 since the last rescale, so most steps only produce P.
+    const int t = warp >> 2;
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int pos = pos0 + t * TC_BQ + r;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tmem_s = tmem_base + t * TC_BK + lane_addr;
+    const uint32_t tmem_o = tmem_base + 2 * TC_BK + t * 128 + lane_addr;
+    uint8_t* p_row = p_sm + t * P_BYTES + r * 128;
+    const int n_mine = n_tile[t];
+    float m_ref = -INFINITY, l_run = 0.f;
+    pdl_wait();
+    bool ok = true;
+    for (int i = 0; i < n_mine && ok; ++i) {
+      ok = mbar_wait(&s_ready[t], i & 1, abort);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int j0 = (page_lo + 2 * i) * SB_PAGE_TOKENS;
+      const bool edge = j0 + TC_BK - 1 > pos0 + t * TC_BQ ||
+                        (window > 0 && j0 <= pos0 + t * TC_BQ + TC_BQ - window);
+      // first pass: the row's maximum; the second half of the row stays in registers
+      float sv[64];
+      float mx = -INFINITY;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        tmem_load64(tmem_s + h * 64, sv);
+        if (edge) {
+#pragma unroll
+          for (int e = 0; e < 64; ++e) {
+            const int j = j0 + h * 64 + e;
+            if (j > pos || (window > 0 && j <= pos - window)) sv[e] = -INFINITY;
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < 64; ++e) mx = fmaxf(mx, sv[e]);
+      }
+      mx *= scale_log2;                               // scale_log2 > 0: the maximum commutes with it
+      // the softmax of step i needs PV of step i-1 finished: it reads P's tile and adds to O
+      if (i > 0) {
+        ok = mbar_wait(&o_ready[t], (i - 1) & 1, abort);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      }
+      const bool grow = m_ref != -INFINITY && mx > m_ref + 8.f;
+      if (__any_sync(0xffffffffu, grow)) {
+        const float m_new = fmaxf(m_ref, mx);
+        const float alpha = m_ref == -INFINITY ? 1.f : fast_exp2(m_ref - m_new);
+        l_run *= alpha;
+        m_ref = m_new;
+#pragma unroll 1
+        for (int c = 0; c < D; c += 32) {
+          float ov[32];
+          tmem_load32(tmem_o + c, ov);
+#pragma unroll
+          for (int e = 0; e < 32; ++e) ov[e] *= alpha;
+          tmem_store32(tmem_o + c, ov);
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      } else if (m_ref == -INFINITY) {
+        m_ref = mx;                                   // nothing accumulated yet for this row
+      }
+      const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+      // second pass: P = exp2(S * scale - m), rounded to bfloat16, into the A operand tile
+      // (K-major: 64-key chunk h, 16-byte column c ^ (r % 8) of row r); half 1 first, it is at hand
+      float rs = 0.f;
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        const int h = 1 - hh;
+        if (hh == 1) {
+          tmem_load64(tmem_s, sv);
+          if (edge) {
+#pragma unroll
+            for (int e = 0; e < 64; ++e) {
+              const int j = j0 + e;
+              if (j > pos || (window > 0 && j <= pos - window)) sv[e] = -INFINITY;
+            }
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {                  // 16-byte columns of 8 keys
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float p0 = fast_exp2(fmaf(sv[c * 8 + 2 * e], scale_log2, -m_use));
+            const float p1 = fast_exp2(fmaf(sv[c * 8 + 2 * e + 1], scale_log2, -m_use));
+            rs += p0 + p1;
+            __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+            w[e] = *reinterpret_cast<uint32_t*>(&pk);
+          }
+          *reinterpret_cast<uint4*>(p_row + h * SUB + ((c ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+      l_run += rs;
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_ready[t]);
+    }
+    if (ok && n_mine > 0) ok = mbar_wait(&o_ready[t], (n_mine - 1) & 1, abort);
+    if (ok && n_mine > 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const float inv = 1.f / l_run;
+      const bool valid = t * TC_BQ + r < rows_valid;
+      bf16* dst = out + ((size_t)seq_q_start[seq] + q_first + t * TC_BQ + r) * ((size_t)heads * D) + (size_t)head * D;
+#pragma unroll 1
+      for (int c = 0; c < D; c += 32) {
+        float ov[32];
+        tmem_load32(tmem_o + c, ov);
+        if (valid) {
+#pragma unroll
+          for (int d = 0; d < 32; d += 8) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              __nv_bfloat162 pk = __floats2bfloat162_rn(ov[d + 2 * e] * inv, ov[d + 2 * e + 1] * inv);
+              w[e] = *reinterpret_cast<uint32_t*>(&pk);
+            }
+            *reinterpret_cast<uint4*>(dst + c + d) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 9) {
+    __syncwarp();
+    tmem_free(tmem_holder, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && abort_flag && status) atomicOr(status, 16);
+}
+
+// ------------------------------------------------------------------------------------------ host
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// A [rows, cols] row-major bfloat16 matrix read in boxes of [box_rows x 64] with 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return -3;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims, strides, box, elem,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS ? 0 : -4;
+}
+
+template <int D>
+static int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out,
+                  const int* block_table, int table_stride, const int* seq_slot, const int* seq_q_start,
+                  const int* seq_q_len, const int* seq_kv_len, const int* tile_seq, const int* tile_first,
+                  int n_tiles, int heads, int kv_heads, float scale, int window, int* status, cudaStream_t s) {
+  constexpr int DC = D / 64;
+  const int smem = (2 * DC + 4 + TC_RING * DC) * 128 * 128 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  return launch_dependent(attention_prefill_tc_kernel<D>, dim3(heads, n_tiles), dim3(TC_THREADS), smem, s, mq, mk,
+                          mv, (bf16*)out, block_table, table_stride, seq_slot, seq_q_start, seq_q_len, seq_kv_len,
+                          tile_seq, tile_first, heads, kv_heads, scale * 1.4426950408889634f, window, status);
+}
+
+extern "C" {
+
+// Same contract as sb_attention_prefill; n_tokens rows in q/out, n_pages pages in the stores.
+// head_dim must be 64 or 128 (returns -2 otherwise).
+int sb_attention_prefill_tc(const void* q, void* out, const void* k_store, const void* v_store,
+                            const int* block_table, int table_stride, const int* seq_slot,
+                            const int* seq_q_start, const int* seq_q_len, const int* seq_kv_len,
+                            const int* tile_seq, const int* tile_first, int n_tiles, int n_tokens,
+                            int n_pages, int heads, int kv_heads, int head_dim, float scale, int window,
+                            int* status, cudaStream_t s) {
+  if (n_tiles == 0) return 0;
+  if (kv_heads <= 0 || heads % kv_heads) return -2;
+  if (head_dim != 64 && head_dim != 128) return -2;
+  if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)k_store | (uintptr_t)v_store) & 15) return -2;
+  CUtensorMap mq, mk, mv;
+  int rc = make_map(&mq, q, n_tokens, (long long)heads * head_dim, TC_BQ);
+  if (rc) return rc;
+  const long long kv_rows = (long long)n_pages * kv_heads * SB_PAGE_TOKENS;
+  rc = make_map(&mk, k_store, kv_rows, head_dim, SB_PAGE_TOKENS);
+  if (rc) return rc;
+  rc = make_map(&mv, v_store, kv_rows, head_dim, SB_PAGE_TOKENS);
+  if (rc) return rc;
+#define ARGS mq, mk, mv, out, block_table, table_stride, seq_slot, seq_q_start, seq_q_len, seq_kv_len, \
+             tile_seq, tile_first, n_tiles, heads, kv_heads, scale, window, status, s
+  if (head_dim == 64) return launch<64>(ARGS);
+  return launch<128>(ARGS);
+#undef ARGS
+}
+
+}  // extern "C"

@@ -38,6 +38,7 @@ SOURCES = (
     "attention_decode_mma",
     "attention_decode_noalloc",
     "attention_prefill",
+    "attention_prefill_tc",
     "linear_small",
     "sgemm",
     "gemm_tcgen05",

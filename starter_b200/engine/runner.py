@@ -191,4 +191,6 @@ class ModelRunner:
                 problems.append("a wait inside the tensor-core product ran out of time")
             if code & 8:
                 problems.append("a wait inside the decode attention kernel ran out of time")
+            if code & 16:
+                problems.append("a wait inside the tensor-core prefill attention kernel ran out of time")
             raise RuntimeError("; ".join(problems) or f"device status {code}")

@@ -331,11 +331,14 @@ PREFILL_HEAD_DIMS = (16, 32, 64, 128)
 
 
 def attention_prefill(q, k_store, v_store, block_table, seq_slot, seq_q_start, seq_q_len, seq_kv_len,
-                      tile_seq, tile_first, heads, kv_heads, head_dim, scale, window=None):
+                      tile_seq, tile_first, heads, kv_heads, head_dim, scale, window=None, status=None,
+                      kernel=None):
     """Causal attention for steps with many tokens per sequence (bfloat16, tensor cores).
 
     ``q`` ``[T, heads * head_dim]`` packed by sequence; the ``seq_*`` arrays describe each sequence
-    of the step, ``tile_seq``/``tile_first`` list the tiles of 64 queries."""
+    of the step, ``tile_seq``/``tile_first`` list the tiles of 64 queries.  Head sizes 64 and 128 run
+    on the tcgen05 kernel (128 queries a block, accumulators in tensor memory), the others on the
+    mma.sync kernel; ``kernel`` ("tcgen05" or "mma") forces one of them."""
     _need(q, "q", torch.bfloat16, 2)
     if q.shape[1] != heads * head_dim:
         raise KernelError(f"q has width {q.shape[1]}, expected {heads * head_dim}")
@@ -352,6 +355,21 @@ def attention_prefill(q, k_store, v_store, block_table, seq_slot, seq_q_start, s
                     ("seq_kv_len", seq_kv_len), ("tile_seq", tile_seq), ("tile_first", tile_first)):
         _need(t, name, torch.int32, 1)
     out = torch.empty_like(q)
+    if kernel is None:
+        kernel = "tcgen05" if head_dim in PREFILL_TC_HEAD_DIMS else "mma"
+    if kernel == "tcgen05":
+        if head_dim not in PREFILL_TC_HEAD_DIMS:
+            raise KernelError(f"the tcgen05 prefill kernel takes head_dim {PREFILL_TC_HEAD_DIMS}, not {head_dim}")
+        if not q.is_contiguous():
+            raise KernelError("q must be contiguous")
+        rc = build.load("attention_prefill_tc").sb_attention_prefill_tc(
+            _ptr(q), _ptr(out), _ptr(k_store), _ptr(v_store), _ptr(block_table), block_table.shape[1],
+            _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), _ptr(seq_kv_len), _ptr(tile_seq),
+            _ptr(tile_first), tile_seq.shape[0], q.shape[0], k_store.shape[0], heads, kv_heads, head_dim,
+            ctypes.c_float(scale), int(window or 0), _ptr(status) if status is not None else None,
+            _stream())
+        _check(rc, "attention_prefill_tc")
+        return out
     rc = build.load("attention_prefill").sb_attention_prefill(
         _ptr(q), _ptr(out), _ptr(k_store), _ptr(v_store), _ptr(block_table), block_table.shape[1],
         _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), _ptr(seq_kv_len), _ptr(tile_seq),
@@ -361,6 +379,7 @@ def attention_prefill(q, k_store, v_store, block_table, seq_slot, seq_q_start, s
     return out
 
 
+PREFILL_TC_HEAD_DIMS = (64, 128)
 DECODE_HEAD_DIMS = (16, 32, 64, 128, 256)
 
 

@@ -82,7 +82,8 @@ class GroupedQueryAttention(Part):
         elif q.dtype == torch.bfloat16 and s.head_dim in ops.PREFILL_HEAD_DIMS:
             a = ops.attention_prefill(q, keys, values, cache.block_table, ctx.seq_slot, ctx.seq_q_start,
                                       ctx.seq_q_len, ctx.seq_kv_len, ctx.tile_seq, ctx.tile_first,
-                                      s.num_heads, s.num_kv_heads, s.head_dim, s.scale, s.window)
+                                      s.num_heads, s.num_kv_heads, s.head_dim, s.scale, s.window,
+                                      status=ctx.status)
         else:
             a = ops.attention_rowwise(q, keys, values, cache.block_table, ctx.tok_slot, ctx.tok_pos,
                                       s.num_heads, s.num_kv_heads, s.head_dim, s.scale, s.window)

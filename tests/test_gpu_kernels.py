@@ -304,18 +304,26 @@ def test_tensor_core_product(rows, n, k, gated, bm, splits):
 
 
 @pytest.mark.parametrize("heads,kv_heads,d,window", [(4, 2, 16, None), (6, 2, 32, 5), (8, 8, 128, None),
-                                                    (8, 1, 64, 70), (32, 8, 128, None), (4, 4, 64, 64)])
-def test_attention_prefill_many_tokens_per_sequence(heads, kv_heads, d, window):
-    """Whole prompts, a chunk that continues a sequence (its first query is not at position 0), one
+                                                    (8, 1, 64, 70), (32, 8, 128, None), (4, 4, 64, 64),
+                                                    (6, 3, 128, 130)])
+@pytest.mark.parametrize("kernel", ["mma", "tcgen05"])
+def test_attention_prefill_many_tokens_per_sequence(heads, kv_heads, d, window, kernel):
+    """Both prefill kernels (mma.sync tiles of 64 queries; tcgen05 tiles of 128 for head sizes 64 and
+    128).  Whole prompts, a chunk that continues a sequence (its first query is not at position 0), one
     query, lengths at and next to the tile and page edges, scattered pages, a far key made to win."""
     from starter_b200 import ops
 
-    lengths, new = [130, 1, 64, 200, 65, 300], [130, 1, 3, 77, 65, 129]
+    if kernel == "tcgen05" and d not in ops.PREFILL_TC_HEAD_DIMS:
+        pytest.skip("the tcgen05 kernel takes head sizes 64 and 128")
+    status = dev(torch.zeros(1, dtype=torch.int32))
+    lengths, new = [130, 1, 64, 200, 65, 300, 450], [130, 1, 3, 77, 65, 129, 450]
     c = attention_case("bfloat16", heads, kv_heads, d, lengths=lengths, new=new, window=window, seed=60, spike=2)
     q_start = [sum(new[:i]) for i in range(len(new))]
     tiles = [(i, f) for i in range(len(new)) for f in range(0, new[i], 64)]
     ints = lambda v: dev(torch.tensor(v, dtype=torch.int32))
     got = ops.attention_prefill(dev(c["q"]), dev(c["ks"]), dev(c["vs"]), dev(c["table"]), ints(list(range(len(new)))),
                                 ints(q_start), ints(new), ints(lengths), ints([t[0] for t in tiles]),
-                                ints([t[1] for t in tiles]), heads, kv_heads, d, c["scale"], window)
+                                ints([t[1] for t in tiles]), heads, kv_heads, d, c["scale"], window,
+                                status=status, kernel=kernel)
+    assert status.item() == 0
     assert torch.allclose(got.cpu().float(), c["want"].float(), atol=2e-2, rtol=2e-2)
