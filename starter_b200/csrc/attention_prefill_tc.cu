@@ -1,29 +1,38 @@
 // Causal grouped-query attention for prompts on the fifth-generation tensor cores (bfloat16).
 //
-// A CTA takes 128 consecutive query tokens of one sequence and one query head.  Both products run as
-// tcgen05.mma with the accumulators in tensor memory:
-//     S   = Q K^T     M = 128 queries, N = 128 keys,     K = head_dim   (K and Q K-major)
-//     O_j = P V       M = 128 queries, N = head_dim,     K = 128 keys   (V as it lies in the cache:
-//                                                                        keys x head_dim, "MN-major")
-// TMA brings Q once and, per step of 128 keys (two cache pages), K and V into a two-stage ring with
-// the 128-byte swizzle the tensor core reads.  Four warps own the 128 rows (thread = query row =
-// TMEM lane): they read S with tcgen05.ld, do the online softmax in float without any shuffle
-// (engine/kernels/fused.py:288-312), write P rounded to bfloat16 (fused.py:699-701) into shared
-// memory as the next A operand, and fold each O_j into the running output held in registers.
-// One thread issues all MMAs; while the softmax warps fold O_j, S of the next step is already being
-// computed.  Keys are read from the cache like in every other attention kernel of this library, so a
-// chunk that continues a sequence needs nothing special: a query at absolute position p sees keys
-// j <= p (engine/engine.py:781-787) and, with a window w, j > p - w.
+// A block takes 256 consecutive query tokens of one sequence and one query head as two tiles of 128.
+// Both products of a tile run as tcgen05.mma with the accumulators in tensor memory:
+//     S  = Q K^T     M = 128 queries, N = 128 keys,  K = head_dim   (Q and K K-major)
+//     O += P V       M = 128 queries, N = head_dim,  K = 128 keys   (V as it lies in the cache:
+//                                                                    keys x head_dim, "MN-major")
+// Tensor memory holds S of both tiles (2 x 128 columns) and O of both tiles (2 x 128 columns).
 //
-// Every wait on an mbarrier gives up after WAIT_LIMIT_NS, raises bit 16 of *status and lets the CTA
-// drain, free its tensor memory and return.
+// Warps:   0-3 softmax of tile 0, 4-7 softmax of tile 1 (thread = query row = TMEM lane, so the
+//          online softmax needs no shuffle: engine/kernels/fused.py:288-312),
+//          8 TMA producer, 9 and 10 the MMA issuers of tile 0 and tile 1.
+// TMA brings both Q tiles once and, per step of 128 keys (two cache pages), K and V with the
+// 128-byte swizzle the tensor core reads; the keys alternate between two buffers and run a step
+// ahead of the values, which have one buffer, because S of step i+1 is issued as soon as the softmax
+// warps have read S of step i out of tensor memory, while PV of step i has to wait for P.
+// The softmax warps write P = exp2(S * scale - m), rounded to bfloat16 (fused.py:699-701), into
+// shared memory as the A operand of PV.  O stays in tensor memory and is accumulated by the MMA
+// itself: m is the reference of the step before as long as no row's maximum outgrows it by more
+// than 2^8 (P stays far inside bfloat16's range, the sum is kept in float); only then is O read,
+// rescaled and written back, and the step's P redone.  The result is O / l, as in the exact online
+// softmax, up to rounding.
+// Keys are read from the cache like in every other attention kernel of this library, so a chunk
+// that continues a sequence needs nothing special: a query at absolute position p sees keys j <= p
+// (engine/engine.py:781-787) and, with a window w, j > p - w.
+//
+// Every wait on an mbarrier gives up after WAIT_LIMIT_NS, raises bit 16 of *status and lets the
+// block drain its copies, free its tensor memory and return.
 #include <cuda.h>
 
 #include "common.cuh"
 
 #define TC_BQ 128
 #define TC_BK 128
-#define TC_THREADS 320
+#define TC_THREADS 352
 #define TC_RING 3
 #define WAIT_LIMIT_NS 2000000000ull
 
@@ -188,8 +197,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* q_sm = smem;                             // 2 tiles
   uint8_t* p_sm = q_sm + 2 * Q_BYTES;               // 2 tiles
-  uint8_t* ring = p_sm + 2 * P_BYTES;               // TC_RING buffers: K0 V0 K1 V1 ... in turn
-  __shared__ uint64_t q_full, full[TC_RING], empty[TC_RING], s_ready[2], p_ready[2], o_ready[2];
+  uint8_t* ring = p_sm + 2 * P_BYTES;               // buffers 0 and 1: keys of even and odd steps; 2: values
+  __shared__ uint64_t q_full, full[TC_RING], empty[TC_RING], s_ready[2], s_free[2], p_ready[2], o_ready[2];
   __shared__ uint32_t tmem_holder;
   __shared__ int abort_flag;
 
@@ -216,10 +225,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
   if (threadIdx.x == 0) {
     mbar_init(&q_full, 1);
-    for (int s = 0; s < TC_RING; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < TC_RING; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 2); }
     for (int t = 0; t < 2; ++t) {
       mbar_init(&s_ready[t], 1);
-      mbar_init(&p_ready[t], 4);      // one arrival per softmax warp
+      mbar_init(&s_free[t], 4);       // one arrival per softmax warp
+      mbar_init(&p_ready[t], 4);
       mbar_init(&o_ready[t], 1);
     }
     abort_flag = 0;
@@ -234,7 +244,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   volatile int* abort = &abort_flag;
 
   if (warp == 8) {
-    // ---------------- producer: Q, then K0 V0 K1 V1 ... through the ring
+    // ---------------- producer
     if (lane == 0) {
       pdl_wait();
       const int q_row0 = seq_q_start[seq] + q_first;
@@ -243,76 +253,92 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       for (int t = 0; t < q_tiles; ++t)
         for (int c = 0; c < DC; ++c)
           tma_load_2d(q_sm + t * Q_BYTES + c * SUB, &map_q, &q_full, head * D + c * 64, q_row0 + t * TC_BQ);
-      int issued = 0;
-      for (int j = 0; j < 2 * n_steps; ++j) {
-        const int b = j % TC_RING, use = j / TC_RING;
-        if (use > 0 && !mbar_wait(&empty[b], (use - 1) & 1, abort)) break;
+      // Keys alternate between buffers 0 and 1 and run a step ahead of the values, which have
+      // buffer 2: K0 V0 K1 | K2 V1 | K3 V2 ...  (S of step i+1 is issued early in step i, PV late.)
+      auto load = [&](bool is_v, int i) -> bool {
+        const int b = is_v ? 2 : (i & 1), use = is_v ? i : (i >> 1);
+        if (use > 0 && !mbar_wait(&empty[b], (use - 1) & 1, abort)) return false;
         mbar_expect_tx(&full[b], KV_BYTES);
-        const CUtensorMap* map = (j & 1) ? &map_v : &map_k;
         for (int half = 0; half < 2; ++half) {
-          const int page = pages[min(page_lo + 2 * (j >> 1) + half, page_hi)];
+          const int page = pages[min(page_lo + 2 * i + half, page_hi)];
           const int row = (page * kv_heads + kvh) * SB_PAGE_TOKENS;
           for (int c = 0; c < DC; ++c)
-            tma_load_2d(ring + b * KV_BYTES + c * SUB + half * 8192, map, &full[b], c * 64, row);
+            tma_load_2d(ring + b * KV_BYTES + c * SUB + half * 8192, is_v ? &map_v : &map_k, &full[b], c * 64, row);
         }
-        issued = j + 1;
+        return true;
+      };
+      int loads[3] = {0, 0, 0};                        // per buffer: how many copies were started
+      bool ok = load(false, 0);
+      if (ok) { loads[0]++; ok = load(true, 0); }
+      if (ok) loads[2]++;
+      if (ok && n_steps > 1) { ok = load(false, 1); if (ok) loads[1]++; }
+      for (int i = 1; i < n_steps && ok; ++i) {
+        if (i + 1 < n_steps) { ok = load(false, i + 1); if (ok) loads[(i + 1) & 1]++; }
+        if (ok) { ok = load(true, i); if (ok) loads[2]++; }
       }
       if (*abort) {                                    // let the copies in flight land before the block ends
-        for (int j = max(issued - TC_RING, 0); j < issued; ++j) {
+        for (int b = 0; b < 3; ++b) {
           const uint64_t start = now_ns();
-          while (!mbar_try(&full[j % TC_RING], (j / TC_RING) & 1) && now_ns() - start < WAIT_LIMIT_NS) {}
+          while (loads[b] > 0 && !mbar_try(&full[b], (loads[b] - 1) & 1) && now_ns() - start < WAIT_LIMIT_NS) {}
         }
       }
     }
-  } else if (warp == 9) {
-    // ---------------- MMA issuer
-    if (lane == 0) {
+  } else if (warp == 9 || warp == 10) {
+    // ---------------- MMA issuers: warp 9 for tile 0, warp 10 for tile 1.  Each runs its own chain
+    // of waits, so that one tile's waiting does not hold up the other's products.
+    const int t = warp - 9, n_mine = n_tile[t], n_other = n_tile[1 - t];
+    if (lane == 0 && n_mine > 0) {
       const uint32_t idesc_s = instr_desc(TC_BK, 0), idesc_o = instr_desc(D, 1);
-      // S_t = Q_t K^T: k runs over the head in steps of 16 (32 bytes inside a 128-byte chunk)
-      auto issue_s = [&](int t, int buf) {
+      const uint32_t q_addr = smem_u32(q_sm + t * Q_BYTES), p_addr = smem_u32(p_sm + t * P_BYTES);
+      // S = Q K^T: k runs over the head in steps of 16 (32 bytes inside a 128-byte chunk)
+      auto issue_s = [&](int buf) {
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k >> 2) * SUB + (k & 3) * 32;
-          umma_bf16(tmem_base + t * TC_BK, smem_desc(smem_u32(q_sm + t * Q_BYTES) + off, 16),
+          umma_bf16(tmem_base + t * TC_BK, smem_desc(q_addr + off, 16),
                     smem_desc(smem_u32(ring + buf * KV_BYTES) + off, 16), idesc_s, k > 0 ? 1u : 0u);
         }
         umma_commit(&s_ready[t]);
       };
-      // O_t (+)= P_t V: k runs over the 128 keys in steps of 16; P K-major (two 64-key chunks); V's
+      // O (+)= P V: k runs over the 128 keys in steps of 16; P K-major (two 64-key chunks); V's
       // rows are keys (16 keys = 2048 bytes), its 64-wide chunks of the head are SUB bytes apart
-      auto issue_pv = [&](int t, int buf, bool first) {
+      auto issue_pv = [&](bool first) {
 #pragma unroll
         for (int k = 0; k < TC_BK / 16; ++k) {
           const uint32_t a_off = (k >> 2) * SUB + (k & 3) * 32;
-          umma_bf16(tmem_base + 2 * TC_BK + t * 128, smem_desc(smem_u32(p_sm + t * P_BYTES) + a_off, 16),
-                    smem_desc(smem_u32(ring + buf * KV_BYTES) + k * 2048, SUB), idesc_o,
+          umma_bf16(tmem_base + 2 * TC_BK + t * 128, smem_desc(p_addr + a_off, 16),
+                    smem_desc(smem_u32(ring + 2 * KV_BYTES) + k * 2048, SUB), idesc_o,
                     (first && k == 0) ? 0u : 1u);
         }
         umma_commit(&o_ready[t]);
       };
+      // A buffer is free after two arrivals, one per tile; a tile that is alone in a step makes both.
+      auto release = [&](int buf, bool alone) {
+        umma_commit(&empty[buf]);
+        if (alone) umma_commit(&empty[buf]);
+      };
       bool ok = mbar_wait(&q_full, 0, abort) && mbar_wait(&full[0], 0, abort);
       if (ok) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        for (int t = 0; t < 2; ++t)
-          if (n_tile[t] > 0) issue_s(t, 0);
-        umma_commit(&empty[0]);
+        issue_s(0);
+        release(0, n_other == 0);
       }
-      for (int i = 0; i < n_steps && ok; ++i) {
-        const int jv = 2 * i + 1, jk = 2 * i + 2;
-        const bool more = i + 1 < n_steps;
-        ok = mbar_wait(&full[jv % TC_RING], (jv / TC_RING) & 1, abort);
-        if (ok && more) ok = mbar_wait(&full[jk % TC_RING], (jk / TC_RING) & 1, abort);
-        for (int t = 0; t < 2 && ok; ++t) {
-          if (i >= n_tile[t]) continue;
-          ok = mbar_wait(&p_ready[t], i & 1, abort);
+      // Step i: S of step i+1 as soon as the softmax warps have read S of step i out of tensor
+      // memory (they are still busy with its exponentials), then PV of step i when P is written.
+      for (int i = 0; i < n_mine && ok; ++i) {
+        if (i + 1 < n_mine) {
+          const int kb = (i + 1) & 1;                  // buffer of K(i+1); V(i) is in buffer 2
+          ok = mbar_wait(&full[kb], ((i + 1) >> 1) & 1, abort) && mbar_wait(&s_free[t], i & 1, abort);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          issue_pv(t, jv % TC_RING, i == 0);
-          if (i + 1 < n_tile[t]) issue_s(t, jk % TC_RING);
+          issue_s(kb);
+          release(kb, i + 1 >= n_other);
         }
+        ok = mbar_wait(&full[2], i & 1, abort) && mbar_wait(&p_ready[t], i & 1, abort);
         if (!ok) break;
-        umma_commit(&empty[jv % TC_RING]);
-        if (more) umma_commit(&empty[jk % TC_RING]);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        issue_pv(i == 0);
+        release(2, i >= n_other);
       }
     }
   } else if (warp < 8) {
@@ -338,11 +364,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const int j0 = (page_lo + 2 * i) * SB_PAGE_TOKENS;
       const bool edge = j0 + TC_BK - 1 > pos0 + t * TC_BQ ||
                         (window > 0 && j0 <= pos0 + t * TC_BQ + TC_BQ - window);
-      // first pass: the row's maximum; the second half of the row stays in registers
       float sv[64];
-      float mx = -INFINITY;
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
+      uint32_t pk[32];
+      float mx = -INFINITY, rs = 0.f;
+      float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+      // half h of the row of S from tensor memory, masked where the step touches an edge
+      auto load_half = [&](int h) {
         tmem_load64(tmem_s + h * 64, sv);
         if (edge) {
 #pragma unroll
@@ -351,63 +378,87 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (j > pos || (window > 0 && j <= pos - window)) sv[e] = -INFINITY;
           }
         }
+      };
+      // P = exp2(S * scale - m) of 8 keys, rounded to bfloat16: one 16-byte column of the A operand
+      auto exp8 = [&](int c, uint32_t* w) {
 #pragma unroll
-        for (int e = 0; e < 64; ++e) mx = fmaxf(mx, sv[e]);
-      }
+        for (int e = 0; e < 4; ++e) {
+          const float p0 = fast_exp2(fmaf(sv[c * 8 + 2 * e], scale_log2, -m_use));
+          const float p1 = fast_exp2(fmaf(sv[c * 8 + 2 * e + 1], scale_log2, -m_use));
+          rs += p0 + p1;
+          __nv_bfloat162 two = __floats2bfloat162_rn(p0, p1);
+          w[e] = *reinterpret_cast<uint32_t*>(&two);
+        }
+      };
+      // K-major A operand: 64-key chunk h, 16-byte column c ^ (r % 8) of row r
+      auto store8 = [&](int h, int c, const uint32_t* w) {
+        *reinterpret_cast<uint4*>(p_row + h * SUB + ((c ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      };
+      auto s_consumed = [&]() {                        // S of this step may be overwritten
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_free[t]);
+      };
+      // One pass in the common case: the exponent's reference is the one of the step before, which
+      // is good as long as no row's maximum outgrows it by more than 2^8.
+      load_half(0);
+#pragma unroll
+      for (int e = 0; e < 64; ++e) mx = fmaxf(mx, sv[e]);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) exp8(c, pk + 4 * c);
+      load_half(1);
+#pragma unroll
+      for (int e = 0; e < 64; ++e) mx = fmaxf(mx, sv[e]);
       mx *= scale_log2;                               // scale_log2 > 0: the maximum commutes with it
-      // the softmax of step i needs PV of step i-1 finished: it reads P's tile and adds to O
-      if (i > 0) {
-        ok = mbar_wait(&o_ready[t], (i - 1) & 1, abort);
+      const bool outgrown = mx > m_ref + 8.f;         // also the first keys a row sees (m_ref = -inf)
+      if (!__any_sync(0xffffffffu, outgrown)) {
+        s_consumed();
+        // P's tile and O are free once PV of the step before has finished
+        if (i > 0) ok = mbar_wait(&o_ready[t], (i - 1) & 1, abort);
         if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      }
-      const bool grow = m_ref != -INFINITY && mx > m_ref + 8.f;
-      if (__any_sync(0xffffffffu, grow)) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) store8(0, c, pk + 4 * c);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          uint32_t w[4];
+          exp8(c, w);
+          store8(1, c, w);
+        }
+      } else {
+        // a new reference: rescale what has been accumulated, then redo this step's P
         const float m_new = fmaxf(m_ref, mx);
         const float alpha = m_ref == -INFINITY ? 1.f : fast_exp2(m_ref - m_new);
+        if (i > 0) {
+          ok = mbar_wait(&o_ready[t], (i - 1) & 1, abort);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+          for (int c = 0; c < D; c += 32) {
+            float ov[32];
+            tmem_load32(tmem_o + c, ov);
+#pragma unroll
+            for (int e = 0; e < 32; ++e) ov[e] *= alpha;
+            tmem_store32(tmem_o + c, ov);
+          }
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        }
         l_run *= alpha;
         m_ref = m_new;
-#pragma unroll 1
-        for (int c = 0; c < D; c += 32) {
-          float ov[32];
-          tmem_load32(tmem_o + c, ov);
+        m_use = m_ref == -INFINITY ? 0.f : m_ref;
+        rs = 0.f;
 #pragma unroll
-          for (int e = 0; e < 32; ++e) ov[e] *= alpha;
-          tmem_store32(tmem_o + c, ov);
-        }
-        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-      } else if (m_ref == -INFINITY) {
-        m_ref = mx;                                   // nothing accumulated yet for this row
-      }
-      const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-      // second pass: P = exp2(S * scale - m), rounded to bfloat16, into the A operand tile
-      // (K-major: 64-key chunk h, 16-byte column c ^ (r % 8) of row r); half 1 first, it is at hand
-      float rs = 0.f;
-#pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        const int h = 1 - hh;
-        if (hh == 1) {
-          tmem_load64(tmem_s, sv);
-          if (edge) {
-#pragma unroll
-            for (int e = 0; e < 64; ++e) {
-              const int j = j0 + e;
-              if (j > pos || (window > 0 && j <= pos - window)) sv[e] = -INFINITY;
-            }
-          }
-        }
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {                  // 16-byte columns of 8 keys
+        for (int c = 0; c < 8; ++c) {
           uint32_t w[4];
+          exp8(c, w);
+          store8(1, c, w);
+        }
+        load_half(0);
+        s_consumed();
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float p0 = fast_exp2(fmaf(sv[c * 8 + 2 * e], scale_log2, -m_use));
-            const float p1 = fast_exp2(fmaf(sv[c * 8 + 2 * e + 1], scale_log2, -m_use));
-            rs += p0 + p1;
-            __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-            w[e] = *reinterpret_cast<uint32_t*>(&pk);
-          }
-          *reinterpret_cast<uint4*>(p_row + h * SUB + ((c ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        for (int c = 0; c < 8; ++c) {
+          uint32_t w[4];
+          exp8(c, w);
+          store8(0, c, w);
         }
       }
       l_run += rs;

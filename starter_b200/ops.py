@@ -332,13 +332,14 @@ PREFILL_HEAD_DIMS = (16, 32, 64, 128)
 
 def attention_prefill(q, k_store, v_store, block_table, seq_slot, seq_q_start, seq_q_len, seq_kv_len,
                       tile_seq, tile_first, heads, kv_heads, head_dim, scale, window=None, status=None,
-                      kernel=None):
+                      kernel=None, max_q_len=None):
     """Causal attention for steps with many tokens per sequence (bfloat16, tensor cores).
 
     ``q`` ``[T, heads * head_dim]`` packed by sequence; the ``seq_*`` arrays describe each sequence
     of the step, ``tile_seq``/``tile_first`` list the tiles of 64 queries.  Head sizes 64 and 128 run
-    on the tcgen05 kernel (128 queries a block, accumulators in tensor memory), the others on the
-    mma.sync kernel; ``kernel`` ("tcgen05" or "mma") forces one of them."""
+    on the tcgen05 kernel (256 queries a block, S and O in tensor memory) when some sequence brings
+    more than 128 queries (``max_q_len``, taken as large when not given); everything else runs on
+    the mma.sync kernel, which has the smaller blocks.  ``kernel`` ("tcgen05" or "mma") forces one."""
     _need(q, "q", torch.bfloat16, 2)
     if q.shape[1] != heads * head_dim:
         raise KernelError(f"q has width {q.shape[1]}, expected {heads * head_dim}")
@@ -356,7 +357,8 @@ def attention_prefill(q, k_store, v_store, block_table, seq_slot, seq_q_start, s
         _need(t, name, torch.int32, 1)
     out = torch.empty_like(q)
     if kernel is None:
-        kernel = "tcgen05" if head_dim in PREFILL_TC_HEAD_DIMS else "mma"
+        long_enough = max_q_len is None or max_q_len > 128
+        kernel = "tcgen05" if head_dim in PREFILL_TC_HEAD_DIMS and long_enough else "mma"
     if kernel == "tcgen05":
         if head_dim not in PREFILL_TC_HEAD_DIMS:
             raise KernelError(f"the tcgen05 prefill kernel takes head_dim {PREFILL_TC_HEAD_DIMS}, not {head_dim}")
