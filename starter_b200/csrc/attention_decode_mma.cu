@@ -43,13 +43,29 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+__device__ __forceinline__ uint32_t cluster_addr(uint32_t addr, uint32_t rank) {
+  uint32_t a;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(addr), "r"(rank));
+  return a;
+}
+__device__ __forceinline__ float cluster_load(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
 template <int D> __device__ __forceinline__ int tile_offset(int row, int chunk) {
   constexpr int C = D / 8;
   const int sw = C >= 8 ? (row & 7) : ((row / (8 / C)) % C);
   return row * D * 2 + ((chunk ^ sw) << 4);
 }
 
-template <int D>
+// CLUSTER: the splits of a row and key/value head are the blocks of one thread-block cluster
+// (cluster dimension z = n_splits <= 8) and merge their results through distributed shared memory,
+// in split order, instead of through the scratch buffers and the merge kernel.
+template <int D, bool CLUSTER>
 __global__ void __launch_bounds__(DM_THREADS)
 attention_decode_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out,
                             const bf16* __restrict__ k_store, const bf16* __restrict__ v_store,
@@ -66,6 +82,7 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out,
   uint8_t* q_tile = smem;                          // [16][D] bfloat16
   uint8_t* ring = smem + DM_ROWS * D * 2;          // DM_STAGES x (keys, values)
   __shared__ float sh_m[DM_WARPS][DM_ROWS], sh_l[DM_WARPS][DM_ROWS];
+  __shared__ float cl_m[DM_ROWS], cl_l[DM_ROWS];   // this block's merged maximum and sum (CLUSTER)
 
   pdl_trigger();
   pdl_wait();
@@ -231,11 +248,35 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out,
     const int head = kvh * groups + g0 + r;
     if (n_splits == 1) {
       out[((size_t)row * heads + head) * D + d] = __float2bfloat16_rn(a / lsum);
+    } else if (CLUSTER) {
+      sh_o[(size_t)r * D + d] = a;      // warp 0's place: (r, d) is read by this thread alone
+      if (d == 0) { cl_m[r] = m_all; cl_l[r] = lsum; }
     } else {
       const size_t slot = ((size_t)row * heads + head) * n_splits + split;
       part_acc[slot * D + d] = a;
       if (d == 0) { part_ml[slot * 2] = m_all; part_ml[slot * 2 + 1] = lsum; }
     }
+  }
+  if (CLUSTER && n_splits > 1) {
+    // out = sum_s w_s acc_s / sum_s w_s l_s with w_s = 2^(m_s - max m), each block a share of (r, d)
+    cluster_sync();
+    const uint32_t acc_addr = smem_u32(sh_o), m_addr = smem_u32(cl_m), l_addr = smem_u32(cl_l);
+    for (int idx = split * DM_THREADS + tid; idx < gc * D; idx += n_splits * DM_THREADS) {
+      const int r = idx / D, d = idx - r * D;
+      float m_all = -INFINITY;
+      for (int sp = 0; sp < n_splits; ++sp) m_all = fmaxf(m_all, cluster_load(cluster_addr(m_addr + r * 4, sp)));
+      float lsum = 0.f, a = 0.f;
+      for (int sp = 0; sp < n_splits; ++sp) {
+        const float ms = cluster_load(cluster_addr(m_addr + r * 4, sp));
+        if (ms != -INFINITY) {
+          const float wgt = exp2f(ms - m_all);
+          lsum += cluster_load(cluster_addr(l_addr + r * 4, sp)) * wgt;
+          a += cluster_load(cluster_addr(acc_addr + (r * D + d) * 4, sp)) * wgt;
+        }
+      }
+      out[((size_t)row * heads + kvh * groups + g0 + r) * D + d] = __float2bfloat16_rn(a / lsum);
+    }
+    cluster_sync();                     // nobody leaves while its shared memory is still read
   }
 }
 
@@ -274,14 +315,21 @@ static int launch(const void* q, void* out, const void* k_store, const void* v_s
   const int smem = DM_ROWS * D * 2 + (RING > MERGE ? RING : MERGE);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attention_decode_mma_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   const int groups = heads / kv_heads;
   const int chunks = (groups + DM_ROWS - 1) / DM_ROWS;
   dim3 grid(rows, kv_heads * chunks, n_splits);
-  int rc = launch_dependent(attention_decode_mma_kernel<D>, grid, dim3(DM_THREADS), smem, s,
+  if (n_splits > 1 && n_splits <= 8)
+    return launch_dependent_cluster(attention_decode_mma_kernel<D, true>, grid, dim3(DM_THREADS), smem, s,
+        dim3(1, 1, n_splits), (const bf16*)q, (bf16*)out, (const bf16*)k_store, (const bf16*)v_store,
+        block_table, table_stride, row_slot, row_kv_len, heads, kv_heads, scale * 1.4426950408889634f,
+        window, n_splits, part_acc, part_ml);
+  int rc = launch_dependent(attention_decode_mma_kernel<D, false>, grid, dim3(DM_THREADS), smem, s,
       (const bf16*)q, (bf16*)out, (const bf16*)k_store, (const bf16*)v_store, block_table, table_stride,
       row_slot, row_kv_len, heads, kv_heads, scale * 1.4426950408889634f, window, n_splits, part_acc,
       part_ml);

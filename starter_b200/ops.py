@@ -382,6 +382,7 @@ def attention_prefill(q, k_store, v_store, block_table, seq_slot, seq_q_start, s
 
 
 PREFILL_TC_HEAD_DIMS = (64, 128)
+DECODE_CLUSTER_SPLITS = 8
 DECODE_HEAD_DIMS = (16, 32, 64, 128, 256)
 
 
@@ -429,7 +430,10 @@ def attention_decode(q, k_store, v_store, block_table, row_slot, row_kv_len, hea
         n_splits = decode_splits(rows, kv_heads, heads // kv_heads, 16 if tensor_cores else 4, kv_hint)
     out = torch.empty_like(q)
     part_acc = part_ml = None
-    if n_splits > 1:
+    # up to DECODE_CLUSTER_SPLITS splits of the tensor-core kernel are one thread-block cluster and
+    # merge through distributed shared memory; more go through scratch and a merge kernel
+    in_cluster = tensor_cores and 1 < n_splits <= DECODE_CLUSTER_SPLITS
+    if n_splits > 1 and not in_cluster:
         part_acc = torch.empty((rows * heads * n_splits * head_dim,), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((rows * heads * n_splits * 2,), dtype=torch.float32, device=q.device)
     if tensor_cores:
@@ -443,7 +447,7 @@ def attention_decode(q, k_store, v_store, block_table, row_slot, row_kv_len, hea
             block_table.shape[1], _ptr(row_slot), _ptr(row_kv_len), rows, heads, kv_heads, head_dim,
             ctypes.c_float(scale), int(window or 0), n_splits, _ptr(part_acc), _ptr(part_ml),
             _ptr(status), _stream())
-    _check(rc, "attention_decode", 2 if n_splits > 1 else 1)
+    _check(rc, "attention_decode", 2 if n_splits > 1 and not in_cluster else 1)
     return out
 
 
