@@ -4,8 +4,16 @@
 // head group, which at large batch costs more time than reading the keys.  Here the query heads that
 // share a key/value head (engine/kernels/fused.py:641-709) form the 16 rows of an mma.sync tile
 // (rows past the group are zero), the keys are its columns, and a key costs a handful of
-// instructions.  Grid (row, kv_head * head_chunks, split) as in the CUDA-core kernel, and the same
-// scratch and merge kernel for the splits (fused.py:729-823).
+// instructions.  Grid (row, kv_head * head_chunks, split) as in the CUDA-core kernel.  Up to 8 splits
+// are the blocks of one thread-block cluster and merge through distributed shared memory; more use
+// the scratch buffers and the merge kernel (fused.py:729-823).
+//
+// FUSED: the kernel takes the q/k/v product's output instead of finished queries and does what
+// rope_cache.cu does for one-token steps itself, with the same arithmetic: each block normalises and
+// rotates its own query heads; a block whose split holds the newest position does the same for the
+// new key, patches key and value into its shared-memory copy of the last page, and the block of the
+// first head chunk also writes them into the cache for the steps to come.  That saves a launch per
+// layer, which at small batch costs more than the arithmetic.
 //
 // A CTA walks the pages of its split.  All four warps copy a page (keys and values, 64 x head_dim
 // each) into a ring of shared-memory stages with 16-byte asynchronous copies, three pages ahead,
@@ -65,14 +73,25 @@ template <int D> __device__ __forceinline__ int tile_offset(int row, int chunk) 
 // CLUSTER: the splits of a row and key/value head are the blocks of one thread-block cluster
 // (cluster dimension z = n_splits <= 8) and merge their results through distributed shared memory,
 // in split order, instead of through the scratch buffers and the merge kernel.
-template <int D, bool CLUSTER>
+struct FusedRope {
+  int q_stride;                 // elements between rows of the q/k/v product's output
+  int has_kv;                   // the output holds keys and values and this layer writes its cache
+  int gain_f32;                 // the head norms' gains are float (else bfloat16)
+  float eps;
+  const void* q_gain;           // may be null: no head norm
+  const void* k_gain;
+  const float* cos_table;       // [positions, D / 2]; may be null: no rotation
+  const float* sin_table;
+};
+
+template <int D, bool CLUSTER, bool FUSED>
 __global__ void __launch_bounds__(DM_THREADS)
 attention_decode_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out,
                             const bf16* __restrict__ k_store, const bf16* __restrict__ v_store,
                             const int* __restrict__ block_table, int table_stride,
                             const int* __restrict__ row_slot, const int* __restrict__ row_kv_len,
                             int heads, int kv_heads, float scale_log2, int window, int n_splits,
-                            float* __restrict__ part_acc, float* __restrict__ part_ml) {
+                            float* __restrict__ part_acc, float* __restrict__ part_ml, const FusedRope fr) {
   constexpr int C = D / 8;
   constexpr int PAGE_BYTES = SB_PAGE_TOKENS * D * 2;
   constexpr int STAGE_BYTES = 2 * PAGE_BYTES;
@@ -83,6 +102,7 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out,
   uint8_t* ring = smem + DM_ROWS * D * 2;          // DM_STAGES x (keys, values)
   __shared__ float sh_m[DM_WARPS][DM_ROWS], sh_l[DM_WARPS][DM_ROWS];
   __shared__ float cl_m[DM_ROWS], cl_l[DM_ROWS];   // this block's merged maximum and sum (CLUSTER)
+  __shared__ __align__(16) bf16 new_kv[2][D];      // the step's own key and value (FUSED)
 
   pdl_trigger();
   pdl_wait();
@@ -107,11 +127,83 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out,
   const int* pages = block_table + (size_t)row_slot[row] * table_stride;
 
   // ---- the group's queries: row r of the tile is head g0 + r; rows past the group are zero
-  for (int idx = tid; idx < DM_ROWS * C; idx += DM_THREADS) {
-    const int r = idx / C, c = idx % C;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < gc) v = *reinterpret_cast<const uint4*>(q + ((size_t)row * heads + (size_t)kvh * groups + g0 + r) * D + c * 8);
-    *reinterpret_cast<uint4*>(q_tile + tile_offset<D>(r, c)) = v;
+  // patch: this block's pages end with the newest position, whose key and value it makes itself
+  const bool patch = FUSED && fr.has_kv && n_pages > 0 && p_end == end_page;
+  if (!FUSED) {
+    for (int idx = tid; idx < DM_ROWS * C; idx += DM_THREADS) {
+      const int r = idx / C, c = idx % C;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (r < gc) v = *reinterpret_cast<const uint4*>(q + ((size_t)row * heads + (size_t)kvh * groups + g0 + r) * D + c * 8);
+      *reinterpret_cast<uint4*>(q_tile + tile_offset<D>(r, c)) = v;
+    }
+  } else {
+    // Head norm and rotation as in rope_cache.cu's 16-byte kernel, sum order included: L lanes share
+    // a head, each with 8 elements of the low half and the 8 they pair with in the high half.
+    constexpr int L = D / 16, HALF = D / 2, PER_PASS = DM_THREADS / L;
+    const int pos = kv_len - 1;
+    const bf16* in_row = q + (size_t)row * fr.q_stride;
+    const int part = tid % L;
+#pragma unroll 1
+    for (int base = 0; base < DM_ROWS + 1; base += PER_PASS) {
+      const int item = base + tid / L;                 // 0..15: query heads; 16: the new key
+      const bool is_k = item == DM_ROWS;
+      const bool valid = is_k ? patch : (item < gc);
+      const bf16* src = in_row + (size_t)(is_k ? heads + kvh : kvh * groups + g0 + item) * D + part * 8;
+      uint4 raw_lo = make_uint4(0, 0, 0, 0), raw_hi = make_uint4(0, 0, 0, 0);
+      if (valid && item <= DM_ROWS) {
+        raw_lo = *reinterpret_cast<const uint4*>(src);
+        raw_hi = *reinterpret_cast<const uint4*>(src + HALF);
+      }
+      float lo[8], hi[8];
+      {
+        const uint32_t wl[4] = {raw_lo.x, raw_lo.y, raw_lo.z, raw_lo.w}, wh[4] = {raw_hi.x, raw_hi.y, raw_hi.z, raw_hi.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          lo[2 * i] = __uint_as_float(wl[i] << 16); lo[2 * i + 1] = __uint_as_float(wl[i] & 0xffff0000u);
+          hi[2 * i] = __uint_as_float(wh[i] << 16); hi[2 * i + 1] = __uint_as_float(wh[i] & 0xffff0000u);
+        }
+      }
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += lo[i] * lo[i] + hi[i] * hi[i];
+#pragma unroll
+      for (int o = L / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      const void* gain = is_k ? fr.k_gain : fr.q_gain;
+      if (valid && gain) {
+        const float inv = rsqrtf(ss / (float)D + fr.eps);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float g_lo = fr.gain_f32 ? ((const float*)gain)[part * 8 + i] : __bfloat162float(((const bf16*)gain)[part * 8 + i]);
+          const float g_hi = fr.gain_f32 ? ((const float*)gain)[HALF + part * 8 + i] : __bfloat162float(((const bf16*)gain)[HALF + part * 8 + i]);
+          lo[i] = rnd<bf16>(rnd<bf16>(lo[i] * inv) * g_lo);
+          hi[i] = rnd<bf16>(rnd<bf16>(hi[i] * inv) * g_hi);
+        }
+      }
+      if (valid && fr.cos_table) {
+        const float* cp = fr.cos_table + (size_t)pos * HALF + part * 8;
+        const float* sp = fr.sin_table + (size_t)pos * HALF + part * 8;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float c = rnd<bf16>(cp[i]), sn = rnd<bf16>(sp[i]);
+          const float a = rnd<bf16>(rnd<bf16>(lo[i] * c) + rnd<bf16>(-hi[i] * sn));
+          const float b = rnd<bf16>(rnd<bf16>(hi[i] * c) + rnd<bf16>(lo[i] * sn));
+          lo[i] = a;
+          hi[i] = b;
+        }
+      }
+      const uint4 out_lo = make_uint4(pack_bf16(lo[0], lo[1]), pack_bf16(lo[2], lo[3]), pack_bf16(lo[4], lo[5]), pack_bf16(lo[6], lo[7]));
+      const uint4 out_hi = make_uint4(pack_bf16(hi[0], hi[1]), pack_bf16(hi[2], hi[3]), pack_bf16(hi[4], hi[5]), pack_bf16(hi[6], hi[7]));
+      if (item < DM_ROWS) {
+        *reinterpret_cast<uint4*>(q_tile + tile_offset<D>(item, part)) = out_lo;
+        *reinterpret_cast<uint4*>(q_tile + tile_offset<D>(item, part + C / 2)) = out_hi;
+      } else if (is_k && valid) {
+        *reinterpret_cast<uint4*>(&new_kv[0][part * 8]) = out_lo;
+        *reinterpret_cast<uint4*>(&new_kv[0][HALF + part * 8]) = out_hi;
+      }
+    }
+    if (patch && tid < C)
+      *reinterpret_cast<uint4*>(&new_kv[1][tid * 8]) =
+          *reinterpret_cast<const uint4*>(in_row + (size_t)(heads + kv_heads + kvh) * D + tid * 8);
   }
   auto load_page = [&](int i) {
     if (i < n_pages) {
@@ -127,7 +219,14 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out,
   };
 #pragma unroll
   for (int i = 0; i < DM_STAGES - 1; ++i) load_page(i);
-  __syncthreads();  // the query tile is written
+  __syncthreads();  // the query tile is written (and the new key and value)
+  if (FUSED && patch && blockIdx.y % chunks == 0 && tid < 2 * C) {
+    // for the steps to come; this step's blocks all patch their own copy instead of reading it back
+    const int pos = kv_len - 1;
+    const size_t at = page_row(pages[end_page - 1], kvh, pos % SB_PAGE_TOKENS, kv_heads, D) + (size_t)(tid % C) * 8;
+    bf16* store = const_cast<bf16*>(tid < C ? k_store : v_store);
+    *reinterpret_cast<uint4*>(store + at) = *reinterpret_cast<const uint4*>(&new_kv[tid < C ? 0 : 1][(tid % C) * 8]);
+  }
 
   uint32_t qf[KSTEPS][4];
   {
@@ -147,6 +246,16 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out,
     __syncthreads();                  // ... and for everyone's
     const uint8_t* kt = ring + (size_t)(i % DM_STAGES) * STAGE_BYTES;
     const uint8_t* vt = kt + PAGE_BYTES;
+    if (FUSED && patch && i == n_pages - 1) {
+      // the newest position's key and value are not in the cache yet (or only just): use our own
+      if (tid < 2 * C) {
+        const int in_page = (kv_len - 1) % SB_PAGE_TOKENS;
+        uint8_t* tile = const_cast<uint8_t*>(tid < C ? kt : vt);
+        *reinterpret_cast<uint4*>(tile + tile_offset<D>(in_page, tid % C)) =
+            *reinterpret_cast<const uint4*>(&new_kv[tid < C ? 0 : 1][(tid % C) * 8]);
+      }
+      __syncthreads();
+    }
     const int j0 = (p_begin + i) * SB_PAGE_TOKENS + warp * 16;   // this warp's 16 keys
 
     float s[2][4];
@@ -304,20 +413,20 @@ __global__ void attention_merge_mma_kernel(const float* __restrict__ part_acc,
   }
 }
 
-template <int D>
-static int launch(const void* q, void* out, const void* k_store, const void* v_store,
-                  const int* block_table, int table_stride, const int* row_slot, const int* row_kv_len,
-                  int rows, int heads, int kv_heads, float scale, int window, int n_splits,
-                  float* part_acc, float* part_ml, cudaStream_t s) {
+template <int D, bool FUSED>
+static int launch_any(const void* q, void* out, const void* k_store, const void* v_store,
+                      const int* block_table, int table_stride, const int* row_slot, const int* row_kv_len,
+                      int rows, int heads, int kv_heads, float scale, int window, int n_splits,
+                      float* part_acc, float* part_ml, const FusedRope& fr, cudaStream_t s) {
   // queries + ring; the ring is reused for the warps' float partial results at the end
   constexpr int RING = DM_STAGES * 2 * SB_PAGE_TOKENS * D * 2;
   constexpr int MERGE = DM_WARPS * DM_ROWS * D * 4;
   const int smem = DM_ROWS * D * 2 + (RING > MERGE ? RING : MERGE);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<D, false, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(attention_decode_mma_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      e = cudaFuncSetAttribute(attention_decode_mma_kernel<D, true, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -325,17 +434,27 @@ static int launch(const void* q, void* out, const void* k_store, const void* v_s
   const int chunks = (groups + DM_ROWS - 1) / DM_ROWS;
   dim3 grid(rows, kv_heads * chunks, n_splits);
   if (n_splits > 1 && n_splits <= 8)
-    return launch_dependent_cluster(attention_decode_mma_kernel<D, true>, grid, dim3(DM_THREADS), smem, s,
+    return launch_dependent_cluster(attention_decode_mma_kernel<D, true, FUSED>, grid, dim3(DM_THREADS), smem, s,
         dim3(1, 1, n_splits), (const bf16*)q, (bf16*)out, (const bf16*)k_store, (const bf16*)v_store,
         block_table, table_stride, row_slot, row_kv_len, heads, kv_heads, scale * 1.4426950408889634f,
-        window, n_splits, part_acc, part_ml);
-  int rc = launch_dependent(attention_decode_mma_kernel<D, false>, grid, dim3(DM_THREADS), smem, s,
+        window, n_splits, part_acc, part_ml, fr);
+  int rc = launch_dependent(attention_decode_mma_kernel<D, false, FUSED>, grid, dim3(DM_THREADS), smem, s,
       (const bf16*)q, (bf16*)out, (const bf16*)k_store, (const bf16*)v_store, block_table, table_stride,
       row_slot, row_kv_len, heads, kv_heads, scale * 1.4426950408889634f, window, n_splits, part_acc,
-      part_ml);
+      part_ml, fr);
   if (rc || n_splits == 1) return rc;
   return launch_dependent(attention_merge_mma_kernel, dim3(rows * heads), dim3(D < 128 ? D : 128), 0, s,
                           (const float*)part_acc, (const float*)part_ml, (bf16*)out, n_splits, D);
+}
+
+template <int D>
+static int launch(const void* q, void* out, const void* k_store, const void* v_store,
+                  const int* block_table, int table_stride, const int* row_slot, const int* row_kv_len,
+                  int rows, int heads, int kv_heads, float scale, int window, int n_splits,
+                  float* part_acc, float* part_ml, cudaStream_t s) {
+  FusedRope none = {};
+  return launch_any<D, false>(q, out, k_store, v_store, block_table, table_stride, row_slot, row_kv_len, rows,
+                              heads, kv_heads, scale, window, n_splits, part_acc, part_ml, none, s);
 }
 
 extern "C" {
@@ -355,6 +474,36 @@ int sb_attention_decode_mma(const void* q, void* out, const void* k_store, const
     case 32: return launch<32>(ARGS);
     case 64: return launch<64>(ARGS);
     case 128: return launch<128>(ARGS);
+    default: return -2;
+  }
+#undef ARGS
+}
+
+// The same for a one-token step straight from the q/k/v product: qkv [rows, q_stride] bfloat16 holds
+// the query heads and, if has_kv, behind them the key and the value heads of each row's new token
+// (position row_kv_len - 1).  Head norm (gains may be null; gain_dtype 0 float, 1 bfloat16), rotation
+// (tables [positions, head_dim / 2] float, may be null) and, if has_kv, the cache write happen here.
+int sb_attention_decode_mma_fused(const void* qkv, int q_stride, void* out, void* k_store, void* v_store,
+                                  const int* block_table, int table_stride, const int* row_slot,
+                                  const int* row_kv_len, int rows, int heads, int kv_heads, int head_dim,
+                                  float scale, int window, int n_splits, float* part_acc, float* part_ml,
+                                  const void* q_gain, const void* k_gain, int gain_dtype, float eps,
+                                  const float* cos_table, const float* sin_table, int has_kv,
+                                  cudaStream_t s) {
+  if (rows == 0) return 0;
+  if (kv_heads <= 0 || heads % kv_heads || n_splits < 1) return -2;
+  if (q_stride % 8 || (((uintptr_t)qkv | (uintptr_t)k_store | (uintptr_t)v_store) & 15)) return -2;
+  if ((cos_table == nullptr) != (sin_table == nullptr)) return -2;
+  FusedRope fr;
+  fr.q_stride = q_stride; fr.has_kv = has_kv; fr.gain_f32 = gain_dtype == 0; fr.eps = eps;
+  fr.q_gain = q_gain; fr.k_gain = k_gain; fr.cos_table = cos_table; fr.sin_table = sin_table;
+#define ARGS qkv, out, k_store, v_store, block_table, table_stride, row_slot, row_kv_len, rows, heads, \
+             kv_heads, scale, window, n_splits, part_acc, part_ml, fr, s
+  switch (head_dim) {
+    case 16: return launch_any<16, true>(ARGS);
+    case 32: return launch_any<32, true>(ARGS);
+    case 64: return launch_any<64, true>(ARGS);
+    case 128: return launch_any<128, true>(ARGS);
     default: return -2;
   }
 #undef ARGS

@@ -403,6 +403,66 @@ def decode_splits(rows: int, kv_heads: int, groups: int, group_rows: int = 4, kv
     return splits
 
 
+def decode_from_qkv_takes(head_dim: int, dtype) -> bool:
+    """Whether ``attention_decode_qkv`` takes this head size and type (the tensor-core decode kernel)."""
+    return dtype == torch.bfloat16 and head_dim in PREFILL_HEAD_DIMS
+
+
+def attention_decode_qkv(qkv, k_store, v_store, block_table, row_slot, row_kv_len, heads, kv_heads, head_dim,
+                         scale, window, q_gain, k_gain, eps, cos_table, sin_table, write_cache=True,
+                         n_splits=None, kv_hint=0):
+    """One-token attention straight from the q/k/v product (bfloat16, tensor cores): head norm,
+    rotation and the cache write of ``qk_norm_rope_store`` happen inside the attention kernel, with
+    the same arithmetic.  Row ``i`` of ``qkv`` is the new token of the sequence in ``row_slot[i]``, at
+    position ``row_kv_len[i] - 1``.  ``qkv`` holds the queries alone when ``write_cache`` is false."""
+    _need(qkv, "qkv", torch.bfloat16, 2)
+    if not decode_from_qkv_takes(head_dim, qkv.dtype):
+        raise KernelError(f"head_dim {head_dim} is not one of {PREFILL_HEAD_DIMS}")
+    if heads % kv_heads:
+        raise KernelError(f"{heads} query heads cannot share {kv_heads} key/value heads")
+    rows = qkv.shape[0]
+    width = (heads + 2 * kv_heads) * head_dim if write_cache else heads * head_dim
+    if qkv.shape[1] != width:
+        raise KernelError(f"qkv has width {qkv.shape[1]}, expected {width}")
+    for store in (k_store, v_store):
+        _need(store, "cache pages", qkv.dtype, 4)
+        if tuple(store.shape[1:]) != (kv_heads, PAGE_TOKENS, head_dim):
+            raise KernelError(f"cache pages have shape {tuple(store.shape)}")
+    _need(block_table, "block_table", torch.int32, 2)
+    _need(row_slot, "row_slot", torch.int32, 1)
+    _need(row_kv_len, "row_kv_len", torch.int32, 1)
+    gain_code = 0
+    if (q_gain is None) != (k_gain is None):
+        raise KernelError("q and k head norms come together")
+    for g in (q_gain, k_gain):
+        if g is not None:
+            _need(g, "head gain", None, 1)
+            if g.shape[0] != head_dim:
+                raise KernelError(f"head gain has {g.shape[0]} entries for head_dim {head_dim}")
+            gain_code = _gain_code(qkv, g)
+    if cos_table is not None:
+        _need(cos_table, "cos_table", torch.float32, 2)
+        _need(sin_table, "sin_table", torch.float32, 2)
+        if cos_table.shape[1] != head_dim // 2 or sin_table.shape != cos_table.shape:
+            raise KernelError("rotary tables must be [positions, head_dim / 2]")
+    if n_splits is None:
+        n_splits = decode_splits(rows, kv_heads, heads // kv_heads, 16, kv_hint)
+    out = torch.empty((rows, heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    part_acc = part_ml = None
+    in_cluster = 1 < n_splits <= DECODE_CLUSTER_SPLITS
+    if n_splits > 1 and not in_cluster:
+        part_acc = torch.empty((rows * heads * n_splits * head_dim,), dtype=torch.float32, device=qkv.device)
+        part_ml = torch.empty((rows * heads * n_splits * 2,), dtype=torch.float32, device=qkv.device)
+    rc = build.load("attention_decode_mma").sb_attention_decode_mma_fused(
+        _ptr(qkv), qkv.shape[1], _ptr(out), _ptr(k_store), _ptr(v_store), _ptr(block_table),
+        block_table.shape[1], _ptr(row_slot), _ptr(row_kv_len), rows, heads, kv_heads, head_dim,
+        ctypes.c_float(scale), int(window or 0), n_splits, _ptr(part_acc), _ptr(part_ml), _ptr(q_gain),
+        _ptr(k_gain), gain_code, ctypes.c_float(eps), _ptr(cos_table), _ptr(sin_table), int(write_cache),
+        _stream())
+    _check(rc, "attention_decode_fused", 2 if n_splits > 1 and not in_cluster else 1)
+    return out
+
+
 def attention_decode(q, k_store, v_store, block_table, row_slot, row_kv_len, heads, kv_heads, head_dim,
                      scale, window=None, n_splits=None, status=None, kv_hint=0):
     """One query per row (the newest token of its sequence) over that sequence's cached keys.

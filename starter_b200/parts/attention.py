@@ -71,6 +71,13 @@ class GroupedQueryAttention(Part):
         qkv = ops.linear(x, weight)
         cos = self.position.cos if self.position is not None else None
         sin = self.position.sin if self.position is not None else None
+        if ctx.max_q_len == 1 and ops.decode_from_qkv_takes(s.head_dim, qkv.dtype):
+            # one token per sequence: head norm, rotation and cache write inside the attention kernel
+            a = ops.attention_decode_qkv(qkv, keys, values, cache.block_table, ctx.seq_slot, ctx.seq_kv_len,
+                                         s.num_heads, s.num_kv_heads, s.head_dim, s.scale, s.window,
+                                         self.q_norm, self.k_norm, s.qk_norm_eps, cos, sin,
+                                         write_cache=writes_cache, kv_hint=ctx.max_kv_len)
+            return ops.linear(a, self.o)
         q = ops.qk_norm_rope_store(
             qkv, s.num_heads, s.num_kv_heads, s.head_dim, self.q_norm, self.k_norm, s.qk_norm_eps,
             cos, sin, ctx.tok_pos, ctx.tok_slot, cache.block_table, keys, values,

@@ -273,6 +273,42 @@ def test_attention_decode_split_over_keys(dtype, heads, kv_heads, d, window, spl
     assert torch.allclose(got.cpu().float(), plain_kernel.cpu().float(), **TOL[dtype])
 
 
+@pytest.mark.parametrize("gain_dtype", ["bfloat16", "float32"])
+@pytest.mark.parametrize("heads,kv_heads,d,window,splits,norm,rope", [
+    (4, 2, 16, None, 1, True, True), (6, 2, 32, 5, 3, True, False), (32, 8, 128, None, None, True, True),
+    (8, 1, 64, 70, 2, False, True), (40, 2, 64, None, 16, True, True)])
+def test_attention_decode_from_qkv_equals_the_separate_kernels(heads, kv_heads, d, window, splits, norm, rope, gain_dtype):
+    """The decode kernel that norms, rotates and files the new key and value itself gives the same
+    bits, in its output and in the cache, as qk_norm_rope_store followed by attention_decode: lengths 1
+    (the new token is the only key), 64 and 65 (it ends or starts a page), 130, 200; scattered pages;
+    also a layer that only reads a cache (queries alone)."""
+    from starter_b200 import ops
+
+    lengths = [130, 1, 64, 65, 200]
+    c = attention_case("bfloat16", heads, kv_heads, d, lengths=lengths, new=[1] * 5, window=window, seed=70)
+    kv_len = dev(torch.tensor(lengths, dtype=torch.int32))
+    slots = dev(torch.arange(5, dtype=torch.int32))
+    pos = dev(torch.tensor([n - 1 for n in lengths], dtype=torch.int32))
+    qkv = dev(rand(5, (heads + 2 * kv_heads) * d, dtype="bfloat16", seed=71))
+    gq = dev(1 + rand(d, dtype=gain_dtype, seed=72, scale=0.2)) if norm else None
+    gk = dev(1 + rand(d, dtype=gain_dtype, seed=73, scale=0.2)) if norm else None
+    cos = dev(torch.cos(rand(256, d // 2, seed=74, scale=3.0))) if rope else None
+    sin = dev(torch.sin(rand(256, d // 2, seed=74, scale=3.0))) if rope else None
+    table = dev(c["table"])
+    for write_cache in (True, False):
+        x = qkv if write_cache else qkv[:, : heads * d].contiguous()
+        ks_a, vs_a, ks_b, vs_b = dev(c["ks"]), dev(c["vs"]), dev(c["ks"]), dev(c["vs"])
+        q = ops.qk_norm_rope_store(x, heads, kv_heads, d, gq, gk, 1e-5, cos, sin, pos, slots, table, ks_a, vs_a,
+                                   write_cache=write_cache)
+        want = ops.attention_decode(q, ks_a, vs_a, table, slots, kv_len, heads, kv_heads, d, c["scale"], window, splits)
+        got = ops.attention_decode_qkv(x, ks_b, vs_b, table, slots, kv_len, heads, kv_heads, d, c["scale"], window,
+                                       gq, gk, 1e-5, cos, sin, write_cache=write_cache, n_splits=splits)
+        assert torch.equal(got, want)
+        assert torch.equal(ks_a, ks_b) and torch.equal(vs_a, vs_b)
+        if write_cache:
+            assert not torch.equal(ks_b.cpu(), c["ks"])      # the new keys went in
+
+
 @pytest.mark.parametrize("rows,n,k,gated,bm,splits", [
     (1, 128, 64, False, 16, 1), (8, 256, 512, False, 16, 2), (5, 300, 1000, False, None, None),
     (16, 2560, 4096, False, None, None), (64, 1000, 2560, False, None, None), (3, 200, 264, False, 16, 5),
