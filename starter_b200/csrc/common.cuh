@@ -26,6 +26,19 @@ template <> __device__ __forceinline__ float from_f<float>(float v) { return v; 
 template <> __device__ __forceinline__ bf16 from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
 
 template <typename T> __device__ __forceinline__ float rnd(float v) { return to_f<T>(from_f<T>(v)); }
+// Two values at once.  For bfloat16 one packed conversion and two integer operations give the same
+// bits as two single conversions, which run on the quarter-rate conversion pipe.
+template <typename T> __device__ __forceinline__ void rnd2(float& a, float& b) { a = rnd<T>(a); b = rnd<T>(b); }
+template <> __device__ __forceinline__ void rnd2<__nv_bfloat16>(float& a, float& b) {
+  __nv_bfloat162 p = __floats2bfloat162_rn(a, b);
+  const uint32_t w = *reinterpret_cast<uint32_t*>(&p);
+  a = __uint_as_float(w << 16);
+  b = __uint_as_float(w & 0xffff0000u);
+}
+// Two floats that already are bfloat16 values, packed (low half first) without a conversion.
+__device__ __forceinline__ uint32_t pack_exact_bf16(float lo, float hi) {
+  return (__float_as_uint(lo) >> 16) | (__float_as_uint(hi) & 0xffff0000u);
+}
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -188,7 +188,15 @@ __global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ act,
     load_vec16<T, N>(gu + row * 2 * inner + col, g);
     load_vec16<T, N>(gu + row * 2 * inner + inner + col, u);
 #pragma unroll
-    for (int j = 0; j < N; ++j) o[j] = rnd<T>(g[j] / (1.f + expf(-g[j]))) * u[j];
+    for (int j = 0; j < N; j += 2) {
+      // the result is rounded to 8 bits of mantissa: the fast exponential and quotient (a few
+      // float ulp, as in the product kernel's gated epilogue) do not show; float keeps the exact ones
+      float s0 = sizeof(T) == 2 ? __fdividef(g[j], 1.f + __expf(-g[j])) : g[j] / (1.f + expf(-g[j]));
+      float s1 = sizeof(T) == 2 ? __fdividef(g[j + 1], 1.f + __expf(-g[j + 1])) : g[j + 1] / (1.f + expf(-g[j + 1]));
+      rnd2<T>(s0, s1);
+      o[j] = s0 * u[j];
+      o[j + 1] = s1 * u[j + 1];
+    }
     store_vec16<T, N>(act + row * inner + col, o);
   }
 }

@@ -89,6 +89,31 @@ __global__ void qk_norm_rope_store_kernel(
   }
 }
 
+// Eight consecutive gains as floats, with 16-byte loads where the pointer allows it.
+__device__ __forceinline__ void load8(const float* p, float* out) {
+  if (((uintptr_t)p & 15) == 0) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w; out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out[i] = p[i];
+  }
+}
+__device__ __forceinline__ void load8(const bf16* p, float* out) {
+  if (((uintptr_t)p & 15) == 0) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      out[2 * i] = __uint_as_float(w[i] << 16);
+      out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out[i] = __bfloat162float(p[i]);
+  }
+}
+
 // The same for bfloat16 with 16-byte accesses: L = head_dim / 16 lanes share a head row, each holding
 // 8 elements of the low half and the 8 they pair with in the high half; a warp takes 32 / L rows.
 template <typename W, int L>
@@ -102,12 +127,12 @@ __global__ void qk_norm_rope_store_vec_kernel(
   pdl_trigger();
   pdl_wait();
   constexpr int HALF = L * 8, D = 2 * HALF;
-  const long long item = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / L;
+  // grid (tokens, blocks of heads): no index needs a division
+  const int token = blockIdx.x;
+  const int head_here = (blockIdx.y * blockDim.x + threadIdx.x) / L;
   const int part = threadIdx.x % L;
-  const bool live = item < n_rows;
-  const long long it = live ? item : 0;
-  const int token = (int)(it / heads_per_token);
-  const int h = (int)(it - (long long)token * heads_per_token);
+  const bool live = head_here < heads_per_token;
+  const int h = live ? head_here : 0;
   const bf16* src = qkv + (size_t)token * row_stride + (size_t)h * D + part * 8;
   const int pos = tok_pos[token];
   const bool is_q = h < heads;
@@ -148,20 +173,36 @@ __global__ void qk_norm_rope_store_vec_kernel(
   if (is_v || !live) return;
   if (gain) {
     const float inv = rsqrtf(ss / (float)D + eps);
+    float g_lo[8], g_hi[8];
+    load8(gain + part * 8, g_lo);
+    load8(gain + HALF + part * 8, g_hi);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      lo[i] = rnd<bf16>(rnd<bf16>(lo[i] * inv) * to_f<W>(gain[part * 8 + i]));
-      hi[i] = rnd<bf16>(rnd<bf16>(hi[i] * inv) * to_f<W>(gain[HALF + part * 8 + i]));
+      float a = lo[i] * inv, b = hi[i] * inv;
+      rnd2<bf16>(a, b);
+      a *= g_lo[i];
+      b *= g_hi[i];
+      rnd2<bf16>(a, b);
+      lo[i] = a;
+      hi[i] = b;
     }
   }
   if (cos_table) {
-    const float* cp = cos_table + (size_t)pos * HALF + part * 8;
-    const float* sp = sin_table + (size_t)pos * HALF + part * 8;
+    // rows of the tables are HALF = 8 L floats: 32-byte aligned pieces
+    const float4* cp4 = reinterpret_cast<const float4*>(cos_table + (size_t)pos * HALF + part * 8);
+    const float4* sp4 = reinterpret_cast<const float4*>(sin_table + (size_t)pos * HALF + part * 8);
+    const float4 c0 = cp4[0], c1 = cp4[1], s0 = sp4[0], s1 = sp4[1];
+    const float cp[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sp[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const float c = rnd<bf16>(cp[i]), sn = rnd<bf16>(sp[i]);
-      const float a = rnd<bf16>(rnd<bf16>(lo[i] * c) + rnd<bf16>(-hi[i] * sn));
-      const float b = rnd<bf16>(rnd<bf16>(hi[i] * c) + rnd<bf16>(lo[i] * sn));
+      float c = cp[i], sn = sp[i];
+      rnd2<bf16>(c, sn);
+      float a0 = lo[i] * c, a1 = -hi[i] * sn, b0 = hi[i] * c, b1 = lo[i] * sn;
+      rnd2<bf16>(a0, a1);
+      rnd2<bf16>(b0, b1);
+      float a = a0 + a1, b = b0 + b1;
+      rnd2<bf16>(a, b);
       lo[i] = a;
       hi[i] = b;
     }
@@ -170,11 +211,9 @@ __global__ void qk_norm_rope_store_vec_kernel(
   {
     uint32_t wl[4], wh[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      __nv_bfloat162 a = __floats2bfloat162_rn(lo[2 * i], lo[2 * i + 1]);
-      __nv_bfloat162 b = __floats2bfloat162_rn(hi[2 * i], hi[2 * i + 1]);
-      wl[i] = *reinterpret_cast<uint32_t*>(&a);
-      wh[i] = *reinterpret_cast<uint32_t*>(&b);
+    for (int i = 0; i < 4; ++i) {             // every value is a bfloat16 already (or came in as one)
+      wl[i] = pack_exact_bf16(lo[2 * i], lo[2 * i + 1]);
+      wh[i] = pack_exact_bf16(hi[2 * i], hi[2 * i + 1]);
     }
     out_lo = make_uint4(wl[0], wl[1], wl[2], wl[3]);
     out_hi = make_uint4(wh[0], wh[1], wh[2], wh[3]);
@@ -193,8 +232,8 @@ static int launch_vec(const void* qkv, void* q_out, const void* q_gain, const vo
   const long long rows = (long long)n_tokens * per_token;
   if (rows == 0) return 0;
   const int threads = 128;
-  const long long blocks = (rows * L + threads - 1) / threads;
-  return launch_dependent(qk_norm_rope_store_vec_kernel<W, L>, dim3((unsigned)blocks), dim3(threads), 0, s,
+  const int head_blocks = (per_token * L + threads - 1) / threads;
+  return launch_dependent(qk_norm_rope_store_vec_kernel<W, L>, dim3((unsigned)n_tokens, (unsigned)head_blocks), dim3(threads), 0, s,
       (const bf16*)qkv, (bf16*)q_out, (const W*)q_gain, (const W*)k_gain, cos_table, sin_table, tok_pos,
       tok_slot, block_table, table_stride, (bf16*)k_store, (bf16*)v_store, rows, heads, kv_heads, eps,
       per_token, row_stride);
@@ -255,7 +294,8 @@ int sb_qk_norm_rope_store(int dtype, int gain_dtype, const void* qkv, void* q_ou
   // bfloat16 with a power-of-two head size and 16-byte aligned rows takes the 16-byte kernel
   const bool pow2 = head_dim >= 16 && head_dim <= 256 && (head_dim & (head_dim - 1)) == 0;
   const bool aligned = row_stride % 8 == 0 && (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_store |
-                                                (uintptr_t)v_store) & 15) == 0;
+                                                (uintptr_t)v_store | (uintptr_t)cos_table |
+                                                (uintptr_t)sin_table) & 15) == 0;
   if (dtype == 1 && pow2 && aligned) {
     if (gain_dtype == 1)
       return launch_vec_by_dim<bf16>(head_dim, qkv, q_out, q_gain, k_gain, cos_table, sin_table, tok_pos,
