@@ -74,10 +74,42 @@ template <typename T, int N> __device__ __forceinline__ void load_vec16(const T*
 }
 template <typename T, int N> __device__ __forceinline__ void store_vec16(T* p, const float* v) {
   uint4 raw;
-  T* e = reinterpret_cast<T*>(&raw);
+  if (sizeof(T) == 2) {                   // packed conversions: half as many on the conversion pipe
+    uint32_t* w = reinterpret_cast<uint32_t*>(&raw);
 #pragma unroll
-  for (int i = 0; i < N; ++i) e[i] = from_f<T>(v[i]);
+    for (int i = 0; i < N / 2; ++i) {
+      __nv_bfloat162 two = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&two);
+    }
+  } else {
+    T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < N; ++i) e[i] = from_f<T>(v[i]);
+  }
   *reinterpret_cast<uint4*>(p) = raw;
+}
+// The same for values that already are values of T (they were rounded): no conversion at all.
+template <typename T, int N> __device__ __forceinline__ void store_exact16(T* p, const float* v) {
+  uint4 raw;
+  if (sizeof(T) == 2) {
+    uint32_t* w = reinterpret_cast<uint32_t*>(&raw);
+#pragma unroll
+    for (int i = 0; i < N / 2; ++i) w[i] = pack_exact_bf16(v[2 * i], v[2 * i + 1]);
+  } else {
+    T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < N; ++i) e[i] = from_f<T>(v[i]);
+  }
+  *reinterpret_cast<uint4*>(p) = raw;
+}
+// N consecutive gains as floats, in one 16-byte load where type and address allow it.
+template <typename W, int N> __device__ __forceinline__ void load_gain(const W* p, float* out) {
+  if (N * sizeof(W) == 16 && ((uintptr_t)p & 15) == 0) {
+    load_vec16<W, N>(p, out);
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i) out[i] = to_f<W>(p[i]);
+  }
 }
 
 template <typename T, typename W, bool ADD, bool WRITE_BACK>
@@ -104,8 +136,12 @@ __global__ void rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ delt
         float d[N];
         load_vec16<T, N>(dr + c, d);
 #pragma unroll
-        for (int i = 0; i < N; ++i) v[it][i] = rnd<T>(v[it][i] + d[i]);
-        if (WRITE_BACK) store_vec16<T, N>(xr + c, v[it]);
+        for (int i = 0; i < N; i += 2) {
+          v[it][i] += d[i];
+          v[it][i + 1] += d[i + 1];
+          rnd2<T>(v[it][i], v[it][i + 1]);
+        }
+        if (WRITE_BACK) store_exact16<T, N>(xr + c, v[it]);
       }
 #pragma unroll
       for (int i = 0; i < N; ++i) ss += v[it][i] * v[it][i];
@@ -117,9 +153,15 @@ __global__ void rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ delt
   for (int it = 0; it < 4; ++it) {
     const int c = (it * blockDim.x + threadIdx.x) * N;
     if (c < hidden) {
-      float o[N];
+      float o[N], gn[N];
+      load_gain<W, N>(gain + c, gn);
 #pragma unroll
-      for (int i = 0; i < N; ++i) o[i] = rnd<T>(v[it][i] * inv) * to_f<W>(gain[c + i]);
+      for (int i = 0; i < N; i += 2) {
+        float a = v[it][i] * inv, b = v[it][i + 1] * inv;
+        rnd2<T>(a, b);
+        o[i] = a * gn[i];
+        o[i + 1] = b * gn[i + 1];
+      }
       store_vec16<T, N>(yr + c, o);
     }
   }
