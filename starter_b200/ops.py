@@ -394,13 +394,23 @@ def decode_attention_takes(head_dim: int, dtype) -> bool:
 
 def decode_splits(rows: int, kv_heads: int, groups: int, group_rows: int = 4, kv_hint: int = 0) -> int:
     """How many parts to cut each row's keys into: as many as keep all blocks resident at once
-    (two per SM), so that no block waits for a second wave, but at least three pages per part when
-    the longest sequence is known (``kv_hint`` tokens)."""
+    (two per SM), so that no block waits for a second wave.
+
+    The tensor-core kernel (``group_rows`` 16) merges up to ``DECODE_CLUSTER_SPLITS`` parts inside a
+    thread-block cluster at no extra launch, so there every part may be as short as a page; beyond
+    that the merge is a kernel of its own, which pays only with twelve parts or more of three pages
+    at least (measured at 1 to 4 rows, 513 to 3,073 keys).  The CUDA-core kernel always merges with a
+    second kernel and wants three pages per part."""
     blocks = rows * kv_heads * (-(-groups // group_rows))
-    splits = max(1, min(32, (2 * 148) // blocks))
-    if kv_hint > 0:
-        splits = max(1, min(splits, -(-kv_hint // (3 * PAGE_TOKENS))))
-    return splits
+    want = max(1, min(32, (2 * 148) // blocks))
+    pages = -(-kv_hint // PAGE_TOKENS) if kv_hint > 0 else None
+    if group_rows < 16:
+        return want if pages is None else max(1, min(want, -(-pages // 3)))
+    in_cluster = want if pages is None else max(1, min(want, pages))
+    if in_cluster <= DECODE_CLUSTER_SPLITS:
+        return in_cluster
+    beyond = want if pages is None else min(want, -(-pages // 3))
+    return beyond if beyond >= 12 else DECODE_CLUSTER_SPLITS
 
 
 def decode_from_qkv_takes(head_dim: int, dtype) -> bool:
