@@ -115,6 +115,8 @@ class GenerationLoop:
                     drawn = runner.step_and_select(entries, self.sampler, temps, now_keys, places)
                 else:
                     drawn = self.sampler.select(runner.step(entries), temps, now_keys, places)
+                if hasattr(drawn, "tolist"):
+                    drawn = drawn.tolist()        # one copy from the device, not one per sequence
                 step_out = {}
                 still = []
                 for i, tok in zip(active, drawn):

@@ -1,4 +1,4 @@
-"""The single-token step captured in CUDA graphs, one per batch size, self-feeding.
+"""The single-token step captured in CUDA graphs, one per batch size and length class, self-feeding.
 
 A decode step at small batch is hundreds of short kernels; launched one by one the
 host is the bottleneck (engine/engine.py:9-12).  The step for ``B`` sequences reads
@@ -11,7 +11,8 @@ Unlike the reference, lengths are per row, and a batch that shrinks simply uses
 the graph of the smaller size.
 
 The graph runs the same model code and kernels as the eager step; it is captured
-the first time a batch size is used.
+the first time a batch size is used at a length class (how the attention cuts a
+sequence's keys into parts is decided at capture, from the class's shortest length).
 """
 
 from __future__ import annotations
@@ -35,11 +36,15 @@ class DecodeGraphs:
         self.ones = torch.ones(max_batch, dtype=torch.int32, device=dev)
         self.zeros = torch.zeros(max_batch, dtype=torch.int32, device=dev)
         self.out = torch.zeros(max_batch, dtype=torch.int32, device=dev)
+        # two pinned staging buffers in turn: a copy may still be reading one when the next is filled
+        self._stage = [torch.zeros((len(self.fields), max_batch), dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._stage_done = [None, None]
+        self._stage_next = 0
         self.graphs = {}
         self.logits = {}
         self.kernels_per_replay = {}  # this library's kernels inside each graph
         self.fed = None  # the slots whose next inputs the device already holds
-        self.kv_hint = 0  # longest sequence of the batch when its graph is captured (sizes the splits)
+        self.kv_hint = 0  # the length the graph being captured is sized for (splits of the attention)
 
     def _field(self, name, batch):
         return self.meta[self.fields.index(name), :batch]
@@ -72,7 +77,7 @@ class DecodeGraphs:
         self.logits.clear()
         self.kernels_per_replay.clear()
 
-    def _capture(self, batch: int) -> None:
+    def _capture(self, batch: int, key) -> None:
         # tables that grow with the sequence are sized for the longest sequence the cache can hold
         # before anything is captured, so that a long generation does not move them mid-way
         cache = self.runner.cache
@@ -94,30 +99,58 @@ class DecodeGraphs:
         graph = torch.cuda.CUDAGraph()
         before = ops.launch_count
         with torch.cuda.graph(graph):
-            self.logits[batch] = self._body(batch)
+            self.logits[key] = self._body(batch)
         self.kernels_per_replay[batch] = ops.launch_count - before
-        self.graphs[batch] = graph
+        self.graphs[key] = graph
         self.meta.copy_(saved)
         torch.cuda.synchronize()
 
     def load(self, slots, tokens, positions, temperatures, keys) -> None:
         """Put a batch's rows on the device (one copy)."""
         batch = len(slots)
-        self.kv_hint = max(positions) + 1
-        host = np.zeros((len(self.fields), batch), dtype=np.int32)
-        host[0] = tokens
-        host[1] = positions
-        host[2] = slots
-        host[3] = np.asarray(positions, dtype=np.int32) + 1
-        host[4] = np.asarray(temperatures, dtype=np.float32).view(np.int32)
-        host[5] = np.asarray(keys, dtype=np.uint32).view(np.int32)
-        pinned = torch.from_numpy(host).pin_memory()
-        self.meta[:, :batch].copy_(pinned, non_blocking=True)
+        turn = self._stage_next
+        self._stage_next = 1 - turn
+        if self._stage_done[turn] is not None:
+            self._stage_done[turn].synchronize()
+        stage = self._stage[turn]
+        host = stage.numpy()
+        host[0, :batch] = tokens
+        host[1, :batch] = positions
+        host[2, :batch] = slots
+        host[3, :batch] = np.asarray(positions, dtype=np.int32) + 1
+        host[4, :batch] = np.asarray(temperatures, dtype=np.float32).view(np.int32)
+        host[5, :batch] = np.asarray(keys, dtype=np.uint32).view(np.int32)
+        self.meta[:, :batch].copy_(stage[:, :batch], non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        self._stage_done[turn] = done
         self.fed = tuple(slots)
 
-    def replay(self, batch: int) -> torch.Tensor:
-        """Run one step for the ``batch`` rows on the device; returns the drawn tokens (device)."""
-        if batch not in self.graphs:
-            self._capture(batch)
-        self.graphs[batch].replay()
+    def replay(self, batch: int, kv_tokens: int = 0) -> torch.Tensor:
+        """Run one step for the ``batch`` rows on the device; returns the drawn tokens (device).
+
+        ``kv_tokens`` is the longest sequence of the batch (this step's token included).  How the
+        attention cuts the keys into parts is fixed when a graph is captured, so there is a graph
+        per batch size and per length class (``hint_pages``); a class's graph assumes the class's
+        shortest length, which keeps every part at a page or more for all lengths of the class."""
+        pages = hint_pages(kv_tokens)
+        key = (batch, pages)
+        if key not in self.graphs:
+            self.kv_hint = pages * ops.PAGE_TOKENS
+            self._capture(batch, key)
+        self.graphs[key].replay()
         return self.out[:batch]
+
+
+#: length classes of the captured decode graphs, in cache pages: powers of two and their 1.5-folds
+HINT_PAGES = tuple(sorted({p for e in range(16) for p in (1 << e, 3 << e >> 1) if p >= 1}))
+
+
+def hint_pages(kv_tokens: int) -> int:
+    """The largest class of ``HINT_PAGES`` that is not longer than ``kv_tokens`` tokens (at least 1)."""
+    pages = max(1, -(-kv_tokens // ops.PAGE_TOKENS))
+    best = 1
+    for p in HINT_PAGES:
+        if p <= pages:
+            best = p
+    return best

@@ -174,8 +174,9 @@ class ModelRunner:
         for s in slots:
             cache.advance(s, 1)
         cache.sync_table()
-        self.prepare(max(cache.lengths[s] for s in slots))
-        return graphs.replay(len(slots))
+        longest = max(cache.lengths[s] for s in slots)
+        self.prepare(longest)
+        return graphs.replay(len(slots), longest)
 
     def check_status(self) -> None:
         """Raise if a kernel flagged a bad input since the last check (reads one int from the device)."""
