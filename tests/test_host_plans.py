@@ -70,3 +70,17 @@ def test_decode_attention_splits_fit_one_wave_and_respect_the_length():
     assert decode_splits(1, 8, 4, 4, kv_hint=513) == 3           # CUDA-core kernel: three pages a part
     for rows in (1, 2, 5, 8, 30, 64):
         assert rows * 8 * decode_splits(rows, 8, 4, 16) <= max(296, rows * 8)
+
+
+def test_decode_graph_length_classes_never_exceed_the_length():
+    """A graph captured for a class assumes the class's shortest length: the class of a length is the
+    largest one not above it, so every part of the attention keeps a page or more."""
+    from starter_b200.engine.graphs import HINT_PAGES, hint_pages
+
+    assert HINT_PAGES[:8] == (1, 2, 3, 4, 6, 8, 12, 16)
+    for tokens in (0, 1, 64, 65, 128, 129, 200, 3073, 4096, 100_000):
+        pages = max(1, -(-tokens // 64))
+        got = hint_pages(tokens)
+        assert got in HINT_PAGES and got <= pages
+        assert all(p > pages for p in HINT_PAGES if p > got)
+    assert [hint_pages(t) for t in (1, 65, 130, 3073)] == [1, 2, 3, 48]
