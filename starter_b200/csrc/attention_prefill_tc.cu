@@ -154,6 +154,19 @@ __device__ __forceinline__ void tmem_store32(uint32_t taddr, const float* v) {
         "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
       : "memory");
 }
+// Two fused multiply-adds / two adds in one instruction (packed f32x2): half the issue slots.
+__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, float b, float c) {
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmov.b64 rc, {%5, %5};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+__device__ __forceinline__ void add2(float& acc0, float& acc1, float a0, float a1) {
+  asm("{\n\t.reg .b64 ra, rb;\n\t"
+      "mov.b64 ra, {%0, %1};\n\tmov.b64 rb, {%2, %3};\n\t"
+      "add.rn.f32x2 ra, ra, rb;\n\tmov.b64 {%0, %1}, ra;\n\t}"
+      : "+f"(acc0), "+f"(acc1) : "f"(a0), "f"(a1));
+}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -366,7 +379,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                         (window > 0 && j0 <= pos0 + t * TC_BQ + TC_BQ - window);
       float sv[64];
       uint32_t pk[32];
-      float mx = -INFINITY, rs = 0.f;
+      float mx = -INFINITY, rs = 0.f, rs_hi = 0.f;   // the row sum in two halves (packed adds)
       float m_use = m_ref == -INFINITY ? 0.f : m_ref;
       // half h of the row of S from tensor memory, masked where the step touches an edge
       auto load_half = [&](int h) {
@@ -383,9 +396,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       auto exp8 = [&](int c, uint32_t* w) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float p0 = fast_exp2(fmaf(sv[c * 8 + 2 * e], scale_log2, -m_use));
-          const float p1 = fast_exp2(fmaf(sv[c * 8 + 2 * e + 1], scale_log2, -m_use));
-          rs += p0 + p1;
+          float x0, x1;
+          fma2(x0, x1, sv[c * 8 + 2 * e], sv[c * 8 + 2 * e + 1], scale_log2, -m_use);
+          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+          add2(rs, rs_hi, p0, p1);
           __nv_bfloat162 two = __floats2bfloat162_rn(p0, p1);
           w[e] = *reinterpret_cast<uint32_t*>(&two);
         }
@@ -446,6 +460,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         m_ref = m_new;
         m_use = m_ref == -INFINITY ? 0.f : m_ref;
         rs = 0.f;
+        rs_hi = 0.f;
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           uint32_t w[4];
@@ -461,7 +476,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           store8(0, c, w);
         }
       }
-      l_run += rs;
+      l_run += rs + rs_hi;
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
