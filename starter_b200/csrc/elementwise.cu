@@ -112,13 +112,24 @@ template <typename W, int N> __device__ __forceinline__ void load_gain(const W* 
   }
 }
 
-template <typename T, typename W, bool ADD, bool WRITE_BACK>
+template <typename T, typename W, bool ADD, bool WRITE_BACK, bool EARLY>
 __global__ void rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ delta,
                                    const W* __restrict__ gain, T* __restrict__ y,
                                    const int* __restrict__ rows, int hidden, float eps) {
   constexpr int N = Vec16<T>::N;
   __shared__ float scratch[33];
   pdl_trigger();
+  // EARLY (few rows, where the launch chain's latency is what counts): the gains are weights, they
+  // do not depend on the kernel before this one and are on their way while it finishes.  With many
+  // rows the registers they would hold are worth more.
+  float gn[EARLY ? 4 : 1][N];
+  if (EARLY) {
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int c = (it * blockDim.x + threadIdx.x) * N;
+      if (c < hidden) load_gain<W, N>(gain + c, gn[it]);
+    }
+  }
   pdl_wait();
   const int out_row = blockIdx.x;
   const int in_row = rows ? rows[out_row] : out_row;
@@ -153,14 +164,15 @@ __global__ void rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ delt
   for (int it = 0; it < 4; ++it) {
     const int c = (it * blockDim.x + threadIdx.x) * N;
     if (c < hidden) {
-      float o[N], gn[N];
-      load_gain<W, N>(gain + c, gn);
+      float o[N];
+      if (!EARLY) load_gain<W, N>(gain + c, gn[0]);
+      const float* g = gn[EARLY ? it : 0];
 #pragma unroll
       for (int i = 0; i < N; i += 2) {
         float a = v[it][i] * inv, b = v[it][i + 1] * inv;
         rnd2<T>(a, b);
-        o[i] = a * gn[i];
-        o[i + 1] = b * gn[i + 1];
+        o[i] = a * g[i];
+        o[i + 1] = b * g[i + 1];
       }
       store_vec16<T, N>(yr + c, o);
     }
@@ -182,11 +194,12 @@ static int launch_rmsnorm(void* x, const void* delta, const void* gain, void* y,
     int vt = 32;
     while (vt * N * 2 < hidden && vt < 1024) vt *= 2;   // about two vectors per thread
     while (vt * N * 4 < hidden) vt *= 2;
-    if (delta && !rows)
-      return launch_dependent(rmsnorm_vec_kernel<T, W, true, true>, dim3(n_rows), dim3(vt), 0, s, xp, dp, gp, yp, rows, hidden, eps);
-    if (delta)
-      return launch_dependent(rmsnorm_vec_kernel<T, W, true, false>, dim3(n_rows), dim3(vt), 0, s, xp, dp, gp, yp, rows, hidden, eps);
-    return launch_dependent(rmsnorm_vec_kernel<T, W, false, false>, dim3(n_rows), dim3(vt), 0, s, xp, dp, gp, yp, rows, hidden, eps);
+#define VEC_LAUNCH(A, B, E) launch_dependent(rmsnorm_vec_kernel<T, W, A, B, E>, dim3(n_rows), dim3(vt), 0, s, xp, dp, gp, yp, rows, hidden, eps)
+    const bool early = n_rows <= 256;
+    if (delta && !rows) return early ? VEC_LAUNCH(true, true, true) : VEC_LAUNCH(true, true, false);
+    if (delta) return early ? VEC_LAUNCH(true, false, true) : VEC_LAUNCH(true, false, false);
+    return early ? VEC_LAUNCH(false, false, true) : VEC_LAUNCH(false, false, false);
+#undef VEC_LAUNCH
   }
   if (delta && !rows)
     return launch_dependent(rmsnorm_kernel<T, W, true, true>, dim3(n_rows), dim3(threads), 0, s, xp, dp, gp, yp, rows, hidden, eps);
