@@ -38,7 +38,11 @@ class DecodeGraphs:
         self.out = torch.zeros(max_batch, dtype=torch.int32, device=dev)
         # two pinned staging buffers in turn: a copy may still be reading one when the next is filled
         self._stage = [torch.zeros((len(self.fields), max_batch), dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._stage_np = [t.numpy() for t in self._stage]
+        self._stage_f32 = [a.view(np.float32) for a in self._stage_np]
+        self._stage_u32 = [a.view(np.uint32) for a in self._stage_np]
         self._stage_done = [None, None]
+        self._views = {}
         self._stage_next = 0
         self.graphs = {}
         self.logits = {}
@@ -110,20 +114,23 @@ class DecodeGraphs:
         batch = len(slots)
         turn = self._stage_next
         self._stage_next = 1 - turn
-        if self._stage_done[turn] is not None:
-            self._stage_done[turn].synchronize()
-        stage = self._stage[turn]
-        host = stage.numpy()
+        done = self._stage_done[turn]
+        if done is None:
+            done = self._stage_done[turn] = torch.cuda.Event()
+        else:
+            done.synchronize()            # the copy that last read this buffer has long finished
+        host = self._stage_np[turn]
         host[0, :batch] = tokens
         host[1, :batch] = positions
         host[2, :batch] = slots
-        host[3, :batch] = np.asarray(positions, dtype=np.int32) + 1
-        host[4, :batch] = np.asarray(temperatures, dtype=np.float32).view(np.int32)
-        host[5, :batch] = np.asarray(keys, dtype=np.uint32).view(np.int32)
-        self.meta[:, :batch].copy_(stage[:, :batch], non_blocking=True)
-        done = torch.cuda.Event()
+        host[3, :batch] = host[1, :batch] + 1
+        self._stage_f32[turn][4, :batch] = temperatures
+        self._stage_u32[turn][5, :batch] = keys
+        views = self._views.get((turn, batch))
+        if views is None:
+            views = self._views[(turn, batch)] = (self.meta[:, :batch], self._stage[turn][:, :batch])
+        views[0].copy_(views[1], non_blocking=True)
         done.record()
-        self._stage_done[turn] = done
         self.fed = tuple(slots)
 
     def replay(self, batch: int, kv_tokens: int = 0) -> torch.Tensor:
