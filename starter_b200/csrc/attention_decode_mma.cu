@@ -64,6 +64,10 @@ __device__ __forceinline__ float cluster_load(uint32_t addr) {
 __device__ __forceinline__ void cluster_sync() {
   asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
 }
+// A rendezvous that publishes nothing (a releasing arrive would first wait for the output's stores).
+__device__ __forceinline__ void cluster_rendezvous() {
+  asm volatile("barrier.cluster.arrive.relaxed;\n\tbarrier.cluster.wait;" ::: "memory");
+}
 template <int D> __device__ __forceinline__ int tile_offset(int row, int chunk) {
   constexpr int C = D / 8;
   const int sw = C >= 8 ? (row & 7) : ((row / (8 / C)) % C);
@@ -385,7 +389,7 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out,
       }
       out[((size_t)row * heads + kvh * groups + g0 + r) * D + d] = __float2bfloat16_rn(a / lsum);
     }
-    cluster_sync();                     // nobody leaves while its shared memory is still read
+    cluster_rendezvous();               // nobody leaves while its shared memory is still read
   }
 }
 

@@ -157,6 +157,11 @@ __device__ __forceinline__ float4 ld_cluster4(uint32_t addr) {
 __device__ __forceinline__ void cluster_sync() {
   asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
 }
+// The same without publishing anything: a rendezvous only.  (A releasing arrive first waits for this
+// thread's earlier global stores to be performed, about a microsecond after the output is written.)
+__device__ __forceinline__ void cluster_rendezvous() {
+  asm volatile("barrier.cluster.arrive.relaxed;\n\tbarrier.cluster.wait;" ::: "memory");
+}
 
 struct GemmArgs {
   void* out;            // [rows, n_out] bfloat16 or float
@@ -364,8 +369,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
       }
     }
-    // nobody leaves (and gives up its shared memory) while a neighbour may still read it
-    if (args.splits > 1) cluster_sync();
+    // nobody leaves (and gives up its shared memory) while a neighbour may still read it; the reads
+    // of a thread have returned when it gets here, because its sums needed them
+    if (args.splits > 1) cluster_rendezvous();
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
