@@ -27,6 +27,8 @@
 #define DM_THREADS (DM_WARPS * 32)
 #define DM_STAGES 3
 #define DM_ROWS 16
+#define DM_TABLE_CACHE 512
+#define DM_CLUSTER_MAX 8
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
@@ -107,9 +109,9 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out,
   __shared__ float sh_m[DM_WARPS][DM_ROWS], sh_l[DM_WARPS][DM_ROWS];
   __shared__ float cl_m[DM_ROWS], cl_l[DM_ROWS];   // this block's merged maximum and sum (CLUSTER)
   __shared__ __align__(16) bf16 new_kv[2][D];      // the step's own key and value (FUSED)
+  __shared__ int sh_pages[DM_TABLE_CACHE];         // the row's page table
 
   pdl_trigger();
-  pdl_wait();
   const int groups = heads / kv_heads;
   const int chunks = (groups + DM_ROWS - 1) / DM_ROWS;
   const int row = blockIdx.x;
@@ -119,6 +121,39 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out,
   const int split = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
+  // Before the dependent-launch wait only what the host wrote before the step's first kernel (the
+  // row's slot and its page table, copied into shared memory) and weights (the gains) are read.  The
+  // row's length is not among them: the step before advances it, and its last kernel may still run
+  // when this one starts.  After the wait the order is: the length; then, together, the first pages'
+  // copies (page numbers are at hand), the rotation table's row and this thread's share of the
+  // q/k/v product's row; then the arithmetic on what has arrived meanwhile.
+  const int slot = row_slot[row];
+  const int* pages = block_table + (size_t)slot * table_stride;
+  if (table_stride <= DM_TABLE_CACHE) {
+    for (int i = tid; i < table_stride; i += DM_THREADS) sh_pages[i] = pages[i];
+    pages = sh_pages;
+  }
+  constexpr int L = D / 16, HALF = D / 2, PER_PASS = DM_THREADS / L;
+  const int part = tid % L;
+  const bf16* in_row = FUSED ? q + (size_t)row * fr.q_stride : nullptr;
+  // the item of a pass: 0..15 are the tile's query heads, 16 is the new key (FUSED)
+  auto item_source = [&](int item) {
+    return in_row + (size_t)(item == DM_ROWS ? heads + kvh : kvh * groups + g0 + item) * D + part * 8;
+  };
+  auto item_loadable = [&](int item) { return item == DM_ROWS ? fr.has_kv != 0 : item < gc; };
+  float gq_lo[8], gq_hi[8];
+  if (FUSED) {
+    const void* gain = tid / L == DM_ROWS ? fr.k_gain : fr.q_gain;
+    if (gain) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        gq_lo[i] = fr.gain_f32 ? ((const float*)gain)[part * 8 + i] : __bfloat162float(((const bf16*)gain)[part * 8 + i]);
+        gq_hi[i] = fr.gain_f32 ? ((const float*)gain)[HALF + part * 8 + i] : __bfloat162float(((const bf16*)gain)[HALF + part * 8 + i]);
+      }
+    }
+  }
+  pdl_wait();
+  __syncthreads();                                     // the page table is in shared memory
   const int kv_len = row_kv_len[row];
   int first = 0;
   if (window > 0 && kv_len - window > 0) first = kv_len - window;
@@ -128,11 +163,43 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out,
   const int p_begin = first_page + split * per_split;
   const int p_end = min(p_begin + per_split, end_page);
   const int n_pages = max(p_end - p_begin, 0);
-  const int* pages = block_table + (size_t)row_slot[row] * table_stride;
-
-  // ---- the group's queries: row r of the tile is head g0 + r; rows past the group are zero
   // patch: this block's pages end with the newest position, whose key and value it makes itself
   const bool patch = FUSED && fr.has_kv && n_pages > 0 && p_end == end_page;
+  const int pos = kv_len - 1;
+
+  int first_pages[DM_STAGES - 1];
+#pragma unroll
+  for (int i = 0; i < DM_STAGES - 1; ++i) first_pages[i] = i < n_pages ? pages[p_begin + i] : 0;
+  float cs[8], sn[8];
+  if (FUSED && fr.cos_table) {
+    const float* cp = fr.cos_table + (size_t)pos * HALF + part * 8;
+    const float* sp = fr.sin_table + (size_t)pos * HALF + part * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { cs[i] = cp[i]; sn[i] = sp[i]; }
+  }
+  auto copy_page = [&](int i, int page) {
+    if (i < n_pages) {
+      const size_t base = page_row(page, kvh, 0, kv_heads, D);
+      uint8_t* dst = ring + (size_t)(i % DM_STAGES) * STAGE_BYTES;
+      for (int idx = tid; idx < SB_PAGE_TOKENS * C; idx += DM_THREADS) {
+        const int r = idx / C, c = idx % C;
+        cp_async16(dst + tile_offset<D>(r, c), k_store + base + (size_t)idx * 8);
+        cp_async16(dst + PAGE_BYTES + tile_offset<D>(r, c), v_store + base + (size_t)idx * 8);
+      }
+    }
+    cp_commit();
+  };
+  auto load_page = [&](int i) { copy_page(i, i < n_pages ? pages[p_begin + i] : 0); };
+#pragma unroll
+  for (int i = 0; i < DM_STAGES - 1; ++i) copy_page(i, first_pages[i]);
+  // this thread's share of the product's row for the first pass
+  uint4 raw_lo0 = make_uint4(0, 0, 0, 0), raw_hi0 = make_uint4(0, 0, 0, 0);
+  if (FUSED && item_loadable(tid / L)) {
+    raw_lo0 = *reinterpret_cast<const uint4*>(item_source(tid / L));
+    raw_hi0 = *reinterpret_cast<const uint4*>(item_source(tid / L) + HALF);
+  }
+
+  // ---- the group's queries: row r of the tile is head g0 + r; rows past the group are zero
   if (!FUSED) {
     for (int idx = tid; idx < DM_ROWS * C; idx += DM_THREADS) {
       const int r = idx / C, c = idx % C;
@@ -143,21 +210,28 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out,
   } else {
     // Head norm and rotation as in rope_cache.cu's 16-byte kernel, sum order included: L lanes share
     // a head, each with 8 elements of the low half and the 8 they pair with in the high half.
-    constexpr int L = D / 16, HALF = D / 2, PER_PASS = DM_THREADS / L;
-    const int pos = kv_len - 1;
-    const bf16* in_row = q + (size_t)row * fr.q_stride;
-    const int part = tid % L;
 #pragma unroll 1
     for (int base = 0; base < DM_ROWS + 1; base += PER_PASS) {
-      const int item = base + tid / L;                 // 0..15: query heads; 16: the new key
+      const int item = base + tid / L;
       const bool is_k = item == DM_ROWS;
       const bool valid = is_k ? patch : (item < gc);
-      const bf16* src = in_row + (size_t)(is_k ? heads + kvh : kvh * groups + g0 + item) * D + part * 8;
-      uint4 raw_lo = make_uint4(0, 0, 0, 0), raw_hi = make_uint4(0, 0, 0, 0);
-      if (valid && item <= DM_ROWS) {
-        raw_lo = *reinterpret_cast<const uint4*>(src);
-        raw_hi = *reinterpret_cast<const uint4*>(src + HALF);
+      uint4 raw_lo = raw_lo0, raw_hi = raw_hi0;
+      if (base > 0) {                                  // the first pass's loads are long under way
+        raw_lo = raw_hi = make_uint4(0, 0, 0, 0);
+        if (valid && item <= DM_ROWS) {
+          raw_lo = *reinterpret_cast<const uint4*>(item_source(item));
+          raw_hi = *reinterpret_cast<const uint4*>(item_source(item) + HALF);
+        }
+        const void* gain = is_k ? fr.k_gain : fr.q_gain;
+        if (gain) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            gq_lo[i] = fr.gain_f32 ? ((const float*)gain)[part * 8 + i] : __bfloat162float(((const bf16*)gain)[part * 8 + i]);
+            gq_hi[i] = fr.gain_f32 ? ((const float*)gain)[HALF + part * 8 + i] : __bfloat162float(((const bf16*)gain)[HALF + part * 8 + i]);
+          }
+        }
       }
+      if (!valid) raw_lo = raw_hi = make_uint4(0, 0, 0, 0);
       float lo[8], hi[8];
       {
         const uint32_t wl[4] = {raw_lo.x, raw_lo.y, raw_lo.z, raw_lo.w}, wh[4] = {raw_hi.x, raw_hi.y, raw_hi.z, raw_hi.w};
@@ -172,25 +246,20 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out,
       for (int i = 0; i < 8; ++i) ss += lo[i] * lo[i] + hi[i] * hi[i];
 #pragma unroll
       for (int o = L / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      const void* gain = is_k ? fr.k_gain : fr.q_gain;
-      if (valid && gain) {
+      if (valid && (is_k ? fr.k_gain : fr.q_gain)) {
         const float inv = rsqrtf(ss / (float)D + fr.eps);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          const float g_lo = fr.gain_f32 ? ((const float*)gain)[part * 8 + i] : __bfloat162float(((const bf16*)gain)[part * 8 + i]);
-          const float g_hi = fr.gain_f32 ? ((const float*)gain)[HALF + part * 8 + i] : __bfloat162float(((const bf16*)gain)[HALF + part * 8 + i]);
-          lo[i] = rnd<bf16>(rnd<bf16>(lo[i] * inv) * g_lo);
-          hi[i] = rnd<bf16>(rnd<bf16>(hi[i] * inv) * g_hi);
+          lo[i] = rnd<bf16>(rnd<bf16>(lo[i] * inv) * gq_lo[i]);
+          hi[i] = rnd<bf16>(rnd<bf16>(hi[i] * inv) * gq_hi[i]);
         }
       }
       if (valid && fr.cos_table) {
-        const float* cp = fr.cos_table + (size_t)pos * HALF + part * 8;
-        const float* sp = fr.sin_table + (size_t)pos * HALF + part * 8;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          const float c = rnd<bf16>(cp[i]), sn = rnd<bf16>(sp[i]);
-          const float a = rnd<bf16>(rnd<bf16>(lo[i] * c) + rnd<bf16>(-hi[i] * sn));
-          const float b = rnd<bf16>(rnd<bf16>(hi[i] * c) + rnd<bf16>(lo[i] * sn));
+          const float c = rnd<bf16>(cs[i]), s_ = rnd<bf16>(sn[i]);
+          const float a = rnd<bf16>(rnd<bf16>(lo[i] * c) + rnd<bf16>(-hi[i] * s_));
+          const float b = rnd<bf16>(rnd<bf16>(hi[i] * c) + rnd<bf16>(lo[i] * s_));
           lo[i] = a;
           hi[i] = b;
         }
@@ -209,24 +278,9 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out,
       *reinterpret_cast<uint4*>(&new_kv[1][tid * 8]) =
           *reinterpret_cast<const uint4*>(in_row + (size_t)(heads + kv_heads + kvh) * D + tid * 8);
   }
-  auto load_page = [&](int i) {
-    if (i < n_pages) {
-      const size_t base = page_row(pages[p_begin + i], kvh, 0, kv_heads, D);
-      uint8_t* dst = ring + (size_t)(i % DM_STAGES) * STAGE_BYTES;
-      for (int idx = tid; idx < SB_PAGE_TOKENS * C; idx += DM_THREADS) {
-        const int r = idx / C, c = idx % C;
-        cp_async16(dst + tile_offset<D>(r, c), k_store + base + (size_t)idx * 8);
-        cp_async16(dst + PAGE_BYTES + tile_offset<D>(r, c), v_store + base + (size_t)idx * 8);
-      }
-    }
-    cp_commit();
-  };
-#pragma unroll
-  for (int i = 0; i < DM_STAGES - 1; ++i) load_page(i);
   __syncthreads();  // the query tile is written (and the new key and value)
   if (FUSED && patch && blockIdx.y % chunks == 0 && tid < 2 * C) {
     // for the steps to come; this step's blocks all patch their own copy instead of reading it back
-    const int pos = kv_len - 1;
     const size_t at = page_row(pages[end_page - 1], kvh, pos % SB_PAGE_TOKENS, kv_heads, D) + (size_t)(tid % C) * 8;
     bf16* store = const_cast<bf16*>(tid < C ? k_store : v_store);
     *reinterpret_cast<uint4*>(store + at) = *reinterpret_cast<const uint4*>(&new_kv[tid < C ? 0 : 1][(tid % C) * 8]);
@@ -330,20 +384,28 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out,
     l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
     l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
   }
-  float* sh_o = reinterpret_cast<float*>(ring);    // [warps][16][D] floats, the ring is free now
+  // [warps][16][DP] floats in the ring, which is free now; rows are padded by 8 floats so that the
+  // rows a warp stores at once fall into different banks; rows past the group are not stored
+  constexpr int DP = D + 8;
+  float* sh_o = reinterpret_cast<float*>(ring);
   const int r_a = lane >> 2;
   if ((lane & 3) == 0) {
     sh_m[warp][r_a] = m_run[0]; sh_m[warp][r_a + 8] = m_run[1];
     sh_l[warp][r_a] = l_run[0]; sh_l[warp][r_a + 8] = l_run[1];
   }
+  {
+    float* base = sh_o + ((size_t)warp * DM_ROWS) * DP;
+    const int col0 = (lane & 3) * 2;
+    if (r_a < gc) {
 #pragma unroll
-  for (int n = 0; n < NBLK; ++n) {
-    const int col = n * 8 + (lane & 3) * 2;
-    float* base = sh_o + ((size_t)warp * DM_ROWS) * D;
-    base[(size_t)r_a * D + col] = o[n][0];
-    base[(size_t)r_a * D + col + 1] = o[n][1];
-    base[(size_t)(r_a + 8) * D + col] = o[n][2];
-    base[(size_t)(r_a + 8) * D + col + 1] = o[n][3];
+      for (int n = 0; n < NBLK; ++n)
+        *reinterpret_cast<float2*>(base + (size_t)r_a * DP + n * 8 + col0) = make_float2(o[n][0], o[n][1]);
+    }
+    if (r_a + 8 < gc) {
+#pragma unroll
+      for (int n = 0; n < NBLK; ++n)
+        *reinterpret_cast<float2*>(base + (size_t)(r_a + 8) * DP + n * 8 + col0) = make_float2(o[n][2], o[n][3]);
+    }
   }
   __syncthreads();
   for (int idx = tid; idx < gc * D; idx += DM_THREADS) {
@@ -356,13 +418,13 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out,
     for (int w = 0; w < DM_WARPS; ++w) {
       const float wgt = sh_m[w][r] == -INFINITY ? 0.f : exp2f(sh_m[w][r] - m_all);
       lsum += sh_l[w][r] * wgt;
-      a += sh_o[((size_t)w * DM_ROWS + r) * D + d] * wgt;
+      a += sh_o[((size_t)w * DM_ROWS + r) * DP + d] * wgt;
     }
     const int head = kvh * groups + g0 + r;
     if (n_splits == 1) {
       out[((size_t)row * heads + head) * D + d] = __float2bfloat16_rn(a / lsum);
     } else if (CLUSTER) {
-      sh_o[(size_t)r * D + d] = a;      // warp 0's place: (r, d) is read by this thread alone
+      sh_o[(size_t)r * DP + d] = a;     // warp 0's place: (r, d) is read by this thread alone
       if (d == 0) { cl_m[r] = m_all; cl_l[r] = lsum; }
     } else {
       const size_t slot = ((size_t)row * heads + head) * n_splits + split;
@@ -376,15 +438,27 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out,
     const uint32_t acc_addr = smem_u32(sh_o), m_addr = smem_u32(cl_m), l_addr = smem_u32(cl_l);
     for (int idx = split * DM_THREADS + tid; idx < gc * D; idx += n_splits * DM_THREADS) {
       const int r = idx / D, d = idx - r * D;
+      // all parts' values first (the remote loads are in flight together), then the arithmetic
+      float ms[DM_CLUSTER_MAX], ls[DM_CLUSTER_MAX], as[DM_CLUSTER_MAX];
+#pragma unroll
+      for (int sp = 0; sp < DM_CLUSTER_MAX; ++sp) {
+        if (sp < n_splits) {
+          ms[sp] = cluster_load(cluster_addr(m_addr + r * 4, sp));
+          ls[sp] = cluster_load(cluster_addr(l_addr + r * 4, sp));
+          as[sp] = cluster_load(cluster_addr(acc_addr + (r * DP + d) * 4, sp));
+        }
+      }
       float m_all = -INFINITY;
-      for (int sp = 0; sp < n_splits; ++sp) m_all = fmaxf(m_all, cluster_load(cluster_addr(m_addr + r * 4, sp)));
+#pragma unroll
+      for (int sp = 0; sp < DM_CLUSTER_MAX; ++sp)
+        if (sp < n_splits) m_all = fmaxf(m_all, ms[sp]);
       float lsum = 0.f, a = 0.f;
-      for (int sp = 0; sp < n_splits; ++sp) {
-        const float ms = cluster_load(cluster_addr(m_addr + r * 4, sp));
-        if (ms != -INFINITY) {
-          const float wgt = exp2f(ms - m_all);
-          lsum += cluster_load(cluster_addr(l_addr + r * 4, sp)) * wgt;
-          a += cluster_load(cluster_addr(acc_addr + (r * D + d) * 4, sp)) * wgt;
+#pragma unroll
+      for (int sp = 0; sp < DM_CLUSTER_MAX; ++sp) {
+        if (sp < n_splits && ms[sp] != -INFINITY) {
+          const float wgt = exp2f(ms[sp] - m_all);
+          lsum += ls[sp] * wgt;
+          a += as[sp] * wgt;
         }
       }
       out[((size_t)row * heads + kvh * groups + g0 + r) * D + d] = __float2bfloat16_rn(a / lsum);
@@ -424,7 +498,7 @@ static int launch_any(const void* q, void* out, const void* k_store, const void*
                       float* part_acc, float* part_ml, const FusedRope& fr, cudaStream_t s) {
   // queries + ring; the ring is reused for the warps' float partial results at the end
   constexpr int RING = DM_STAGES * 2 * SB_PAGE_TOKENS * D * 2;
-  constexpr int MERGE = DM_WARPS * DM_ROWS * D * 4;
+  constexpr int MERGE = DM_WARPS * DM_ROWS * (D + 8) * 4;
   const int smem = DM_ROWS * D * 2 + (RING > MERGE ? RING : MERGE);
   static bool configured = false;
   if (!configured) {
@@ -437,7 +511,7 @@ static int launch_any(const void* q, void* out, const void* k_store, const void*
   const int groups = heads / kv_heads;
   const int chunks = (groups + DM_ROWS - 1) / DM_ROWS;
   dim3 grid(rows, kv_heads * chunks, n_splits);
-  if (n_splits > 1 && n_splits <= 8)
+  if (n_splits > 1 && n_splits <= DM_CLUSTER_MAX)
     return launch_dependent_cluster(attention_decode_mma_kernel<D, true, FUSED>, grid, dim3(DM_THREADS), smem, s,
         dim3(1, 1, n_splits), (const bf16*)q, (bf16*)out, (const bf16*)k_store, (const bf16*)v_store,
         block_table, table_stride, row_slot, row_kv_len, heads, kv_heads, scale * 1.4426950408889634f,
