@@ -5,7 +5,8 @@
 Prints one JSON line.  A "step" is one decode step of the whole batch.  ``value`` is decoded
 tokens per second at batch 8, timed on the device with CUDA events around K consecutive steps of
 the captured, self-feeding decode step at the middle of the generation range (context 3,072 of
-4,096); ``e2e`` is the same through ``Engine.generate`` with host token ids in and out every step;
+4,096); ``e2e`` is the same through ``Engine.generate``: host ids out every step, the host-owned inputs
+of every step in from pinned memory, a step launched before the one before it is read;
 ``prefill`` is one 2,048-token prompt; ``points`` are decode at batch 1 and 64; ``roofline`` sets the
 bytes a decode step must read (every weight it uses once, the live requests' keys and values)
 against the measured copy bandwidth.  Every step reads >8 GB of weights, far more than the 126 MB
@@ -96,14 +97,29 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(clocks)}
 
 
-def reference_arm():
-    # The reference is a folder of scripts without packaging metadata, so pip has nothing to install;
-    # its Engine loads weights through a model library whose installed version lacks the attribute
-    # it reads (engine/engine.py:146), and its kernels are Triton.  Recorded in DESIGN.md.
-    print(json.dumps({"impl": "reference", "unavailable":
-                      "alvinyuwen/starter has no setup.py/pyproject (pip install fails) and its "
-                      "Engine needs transformers==4.51.3 (config.rope_theta) which is not installed"}))
-    return 0
+METRIC = "decode tok/s at batch 8 (Qwen3-4B BF16); prefill tok/s at 2,048 tokens; batch 1/64 in points"
+
+
+def config_block(layers: int, batch: int, peaks_source: str) -> dict:
+    """Every size of the run, flat; the same for both arms."""
+    c = QWEN3_4B
+    return {
+        "model": "Qwen3-4B", "layers": layers, "layers_of_model": c["num_hidden_layers"],
+        "hidden": c["hidden_size"], "heads": c["num_attention_heads"], "kv_heads": c["num_key_value_heads"],
+        "head_dim": c["head_dim"], "intermediate": c["intermediate_size"], "vocab": c["vocab_size"],
+        "tied": True, "global_batch": batch, "seq_len": CONTEXT, "prompt_len": PROMPT,
+        "decode_context": DECODE_AT, "parallelism": "single", "l2": "inputs larger than L2",
+        "cache_page": 64, "peaks": peaks_source,
+    }
+
+
+def reference_arm(args) -> int:
+    """The reference's own engine on the same workload (baseline/reference_arm.py)."""
+    from baseline import reference_arm as arm
+
+    sizes = dict(QWEN3_4B, num_hidden_layers=args.layers)
+    return arm.run(args, sizes, CONTEXT, PROMPT, DECODE_AT,
+                   config_block(args.layers, args.batch, peaks()["source"]), ClockSampler(), METRIC)
 
 
 def main() -> int:
@@ -118,7 +134,7 @@ def main() -> int:
     parser.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
     args = parser.parse_args()
     if args.impl == "reference":
-        return reference_arm()
+        return reference_arm(args)
     if args.gpus != 1:
         print(f"bench.py measures one GPU: this library has no multi-GPU path (asked for {args.gpus})")
         return 2
@@ -215,39 +231,44 @@ def main() -> int:
     # ---------------------------------------------------------------- end to end through Engine.generate
     del runner
     torch.cuda.empty_cache()
-    engine = Engine.from_model(model, max_batch=args.batch)
-    e2e_prompts = [prompt(DECODE_AT) for _ in range(args.batch)]
-    stream = engine.generate(e2e_prompts, warmup + steps + 1)
-    next(stream)
-    # host tokens in and out: every step's input ids travel from pinned host memory to the device
-    # (with their positions, slots and sampling settings) and the drawn ids travel back
-    engine.runner.self_feeding = False
-    for _ in range(warmup):
+
+    def e2e_point(batch):
+        """tok/s through the public call: prompts in as host lists, one list of ids out per step."""
+        engine = Engine.from_model(model, max_batch=batch)
+        stream = engine.generate([prompt(DECODE_AT) for _ in range(batch)], warmup + steps + 2)
         next(stream)
-    torch.cuda.synchronize()
-    t0 = time.monotonic()
-    for _ in range(steps):
-        next(stream)
-    torch.cuda.synchronize()
-    t1 = time.monotonic()
-    windows.append((t0, t1))
-    stream.close()
-    e2e_value = args.batch * steps / (t1 - t0)
+        # every step's host-owned inputs (positions, slots, lengths, sampling settings) travel from
+        # pinned host memory to the device and the drawn ids travel back to the host; the ids a step
+        # consumes are the ones the step before drew on the device, so the loop launches a step
+        # before it reads the one before (one step of lookahead, as the reference's loop does)
+        engine.runner.self_feeding = False
+        for _ in range(warmup):
+            next(stream)
+        torch.cuda.synchronize()
+        t0 = time.monotonic()
+        for _ in range(steps):
+            next(stream)
+        torch.cuda.synchronize()
+        t1 = time.monotonic()
+        windows.append((t0, t1))
+        stream.close()
+        engine.runner.check_status()
+        del engine
+        torch.cuda.empty_cache()
+        return batch * steps / (t1 - t0)
+
+    e2e_value = e2e_point(args.batch)
+    if not args.skip_points:
+        points["e2e_b1"] = round(e2e_point(1), 1)
 
     clocks = sampler.stop(windows)
     line = {
-        "metric": "decode tok/s at batch 8 (Qwen3-4B BF16); prefill tok/s at 2,048 tokens; batch 1/64 in points",
+        "metric": METRIC,
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: random weights N(0,0.02), uniform random token ids",
-        "config": {
-            "model": "Qwen3-4B", "layers": args.layers, "layers_of_model": QWEN3_4B["num_hidden_layers"],
-            "hidden": h, "heads": nh, "kv_heads": kv, "head_dim": d, "intermediate": inter, "vocab": vocab,
-            "tied": True, "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT,
-            "decode_context": DECODE_AT, "parallelism": "single", "l2": "inputs larger than L2",
-            "cache_page": 64, "peaks": pk["source"],
-        },
-        "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "h2d_bytes_per_step": 6 * 4 * args.batch,
+        "config": config_block(args.layers, args.batch, pk["source"]),
+        "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "h2d_bytes_per_step": 5 * 4 * args.batch,
                 "d2h_bytes_per_step": 4 * args.batch},
         "gpu_launches": launches,
         "prefill": prefill,

@@ -11,6 +11,15 @@ from dataclasses import dataclass
 from typing import Optional
 
 
+#: tokens per cache page: the one definition; the kernels' own constant is checked against it when
+#: the first kernel library is loaded
+PAGE_TOKENS = 64
+
+
+def pages_for(tokens: int) -> int:
+    return (tokens + PAGE_TOKENS - 1) // PAGE_TOKENS
+
+
 @dataclass(frozen=True)
 class KVNeed:
     """Keys and values per token: ``num_kv_heads * head_dim`` each; ``window`` None = keep all."""

@@ -20,15 +20,9 @@ import numpy as np
 import torch
 
 from .allocator import CacheFull, IndexAllocator
-from .layout import KVNeed, StateNeed, plan_groups
-
-PAGE_TOKENS = 64
+from .layout import PAGE_TOKENS, KVNeed, StateNeed, pages_for, plan_groups
 
 _STATE_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": torch.int32}
-
-
-def pages_for(tokens: int) -> int:
-    return (tokens + PAGE_TOKENS - 1) // PAGE_TOKENS
 
 
 class SequenceCache:
@@ -52,6 +46,13 @@ class SequenceCache:
         self._table_host = np.zeros((max_sequences, per_seq), dtype=np.int32)
         self.block_table = torch.zeros((max_sequences, per_seq), dtype=torch.int32, device=self.device)
         self._dirty = {}  # slot -> (first, last+1) columns of the table not yet on the device
+        # changed table entries travel through pinned staging memory, two buffers in turn, so that
+        # the copies need not block and a buffer is not refilled while a copy may still read it
+        pin = self.device.type == "cuda"
+        self._stage = [torch.zeros((max_sequences * per_seq,), dtype=torch.int32, pin_memory=pin)
+                       for _ in range(2)]
+        self._stage_done = [None, None]
+        self._stage_next = 0
 
         self.groups = plan_groups(kv_needs)
         self._where = {}
@@ -143,10 +144,28 @@ class SequenceCache:
         return list(self._owned[slot])
 
     def sync_table(self) -> None:
-        """Copy block-table rows that changed since the last call to the device."""
+        """Copy block-table entries that changed since the last call to the device (asynchronously,
+        in stream order: kernels launched after this call see them)."""
+        if not self._dirty:
+            return
+        turn = self._stage_next
+        self._stage_next = 1 - turn
+        stage = self._stage[turn]
+        if self.device.type == "cuda":
+            done = self._stage_done[turn]
+            if done is None:
+                done = self._stage_done[turn] = torch.cuda.Event()
+            else:
+                done.synchronize()        # the copies that last read this buffer have long finished
+        at = 0
+        view = stage.numpy()
         for slot, (first, last) in self._dirty.items():
-            src = torch.from_numpy(self._table_host[slot, first:last].copy())
-            self.block_table[slot, first:last].copy_(src, non_blocking=False)
+            n = last - first
+            view[at:at + n] = self._table_host[slot, first:last]
+            self.block_table[slot, first:last].copy_(stage[at:at + n], non_blocking=True)
+            at += n
+        if self.device.type == "cuda":
+            done.record()
         self._dirty.clear()
 
     def check(self) -> None:

@@ -9,6 +9,7 @@ from .spec import (
     RopeSpec,
     ScheduleEntry,
     default_schedule,
+    prenorm_layer,
 )
 
 __all__ = [
@@ -25,5 +26,6 @@ __all__ = [
     "config_from_dict",
     "default_schedule",
     "load_config",
+    "prenorm_layer",
     "register_architecture",
 ]

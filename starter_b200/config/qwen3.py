@@ -21,7 +21,7 @@ from typing import Optional
 from .spec import (
     AttentionSpec,
     GatedFeedForwardSpec,
-    LayerSpec,
+    prenorm_layer,
     ModelSpec,
     NormSpec,
     RopeSpec,
@@ -226,7 +226,7 @@ class Qwen3Config:
                 position=rope,
                 window=window,
             )
-            layers.append(LayerSpec(mixer=mixer, feed_forward=ff, norm1=norm, norm2=norm, names=names))
+            layers.append(prenorm_layer(mixer, ff, norm, norm, names))
         return ModelSpec(
             architecture=self.architecture,
             vocab_size=self.vocab_size,

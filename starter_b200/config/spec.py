@@ -66,18 +66,31 @@ class GatedFeedForwardSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One decoder layer: its mixer, its feed-forward, its two norms and how they are arranged.
+    """One decoder layer: named part specs and the arrangement that puts them together.
 
-    ``names`` maps each part's logical parameter name (``"mixer.q"``,
-    ``"norm1.weight"`` ...) to the tensor name in the checkpoint.
+    ``parts`` maps a part's name inside the layer to its spec.  Which names there are and to which
+    family each belongs (mixer, feed_forward, norm ...) is the arrangement's business: the pre-norm
+    block wants ``mixer``, ``feed_forward``, ``norm1`` and ``norm2``; an arrangement with a third norm,
+    without a feed-forward or with two mixers names its own.  ``names`` maps each part's logical
+    parameter name (``"mixer.q"``, ``"norm1.weight"`` ...) to the tensor name in the checkpoint.
     """
 
-    mixer: object
-    feed_forward: object
-    norm1: object
-    norm2: object
+    parts: dict
     names: dict
     arrangement: str = "prenorm"
+
+    def __getattr__(self, name):
+        # layer.mixer, layer.norm1 ...: the spec of the part of that name
+        parts = object.__getattribute__(self, "parts")
+        if name in parts:
+            return parts[name]
+        raise AttributeError(f"this layer has no part named {name!r} (it has: {', '.join(parts)})")
+
+
+def prenorm_layer(mixer, feed_forward, norm1, norm2, names, arrangement: str = "prenorm") -> LayerSpec:
+    """The layer of the pre-norm block: ``x + mixer(norm1(x))``, then ``+ feed_forward(norm2(.))``."""
+    return LayerSpec({"mixer": mixer, "feed_forward": feed_forward, "norm1": norm1, "norm2": norm2},
+                     names, arrangement)
 
 
 @dataclass(frozen=True)

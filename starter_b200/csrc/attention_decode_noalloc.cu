@@ -29,7 +29,9 @@ int sb_attention_decode_noalloc(const void* q, void* out, const void* k_store, c
     snprintf(message, sizeof message, "heads, head_dim and n_splits must be positive");
     return -2;
   }
-  const long long need = (long long)rows * heads * n_splits * (head_dim + 2);
+  // up to DM_CLUSTER_MAX parts are merged inside a thread-block cluster and touch no scratch at all;
+  // only beyond that are the parts written to the array and merged by a second kernel
+  const long long need = n_splits > DM_CLUSTER_MAX ? (long long)rows * heads * n_splits * (head_dim + 2) : 0;
   if (need > SB_NOALLOC_SCRATCH_FLOATS) {
     snprintf(message, sizeof message,
              "rows * heads * n_splits * (head_dim + 2) = %lld floats of scratch are needed, the static "

@@ -11,9 +11,11 @@
 // What to know before calling it:
 //   * The scratch is ONE static device array of SB_NOALLOC_SCRATCH_FLOATS floats (4 MiB).  Every GPU
 //     on which this library is loaded holds that array until the process exits.
-//   * A call needs rows * heads * n_splits * (head_dim + 2) floats.  More than the array holds is
-//     refused with SB_NOALLOC_TOO_LARGE; sb_attention_decode_noalloc_message() then says how much
-//     was asked for and how much there is.  Nothing is launched in that case.
+//   * A call with more than 8 parts (n_splits) needs rows * heads * n_splits * (head_dim + 2) floats
+//     of it; with up to 8 parts the kernel merges inside a thread-block cluster and uses none.  More
+//     than the array holds is refused with SB_NOALLOC_TOO_LARGE;
+//     sb_attention_decode_noalloc_message() then says how much was asked for and how much there is.
+//     Nothing is launched in that case.
 //   * All calls share the array and it keeps the last call's contents.  Nothing in it has to start at
 //     zero: each call overwrites every entry it later reads (parts that see no key write a neutral
 //     entry).  Two calls that overlap on the GPU (different streams, or graphs replayed together)

@@ -14,6 +14,9 @@
 #include <stdint.h>
 
 #define SB_PAGE_TOKENS 64
+// Every library built from this header says which page size it was compiled for; the Python side
+// compares it with the cache's own constant when it loads the library.
+extern "C" __attribute__((weak, visibility("default"))) int sb_page_tokens() { return SB_PAGE_TOKENS; }
 
 typedef __nv_bfloat16 bf16;
 

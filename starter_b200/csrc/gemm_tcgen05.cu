@@ -17,8 +17,11 @@
 // With `gated`, w is [gate; up] stacked ([2 * n_out, k]); a tile holds 64 gate rows and the matching
 // 64 up rows and the epilogue writes round(silu(gate)) * up (fused.py:89-112).
 //
-// Every wait on an mbarrier gives up after WAIT_LIMIT_NS, raises bit 4 of *status and lets the CTA
-// drain, free its tensor memory and return.
+// Every wait on an mbarrier gives up after a time limit (WAIT_LIMIT_NS unless the caller gives one),
+// raises bit 4 of *status and lets the CTA drain, free its tensor memory and return.  So that this
+// path can be exercised without a fault, the entry point sb_gemm_tcgen05_withheld leaves out one
+// activation copy on purpose: the stage it belongs to never completes, the wait on it runs out and
+// the kernel must come back with the status bit set.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -62,7 +65,8 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
 
 // Bounded wait: false (and *abort set) if the phase did not complete in time or another role gave up.
 // The clock is looked at only now and then: reading it costs more than a try.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort,
+                                          uint64_t limit_ns = WAIT_LIMIT_NS) {
 #pragma unroll 1
   for (int spin = 0; spin < 2048; ++spin)
     if (mbar_try(bar, parity)) return true;
@@ -72,7 +76,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     if (mbar_try(bar, parity)) return true;
     if ((spin & 63) == 0) {
       if (*abort) return false;
-      if (now_ns() - start > WAIT_LIMIT_NS) { *abort = 1; return false; }
+      if (now_ns() - start > limit_ns) { *abort = 1; return false; }
     }
   }
 }
@@ -168,6 +172,8 @@ struct GemmArgs {
   int* status;
   int rows, n_out, k_dim;
   int splits, stages, gated, out_float;
+  unsigned long long wait_limit_ns;   // how long a wait may take before the CTA gives up
+  int withhold_stage;                 // >= 0: the activation copy of this k-block is left out (tests)
 };
 
 template <int BM, bool GATED>
@@ -185,6 +191,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   __shared__ int abort_flag;
 
   const int STAGES = args.stages;
+  const uint64_t limit = args.wait_limit_ns;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = blockIdx.x, split = blockIdx.y, mtile = blockIdx.z;
   const int m0 = mtile * BM;
@@ -232,11 +239,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       }
       pdl_wait();
       for (int i = 0; i < early; ++i)
-        tma_load_2d(smem + (size_t)i * STAGE_BYTES + A_BYTES, &map_x, &full_bar[i], (kb_begin + i) * TILE_K, m0);
+        if (i != args.withhold_stage)
+          tma_load_2d(smem + (size_t)i * STAGE_BYTES + A_BYTES, &map_x, &full_bar[i], (kb_begin + i) * TILE_K, m0);
       issued = early;
       for (int i = early; i < n_kb; ++i) {
         const int s = i % STAGES;
-        if (!mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, abort)) break;
+        if (!mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, abort, limit)) break;
         uint8_t* a = smem + (size_t)s * STAGE_BYTES;
         mbar_expect_tx(&full_bar[s], STAGE_BYTES);
         const int k = (kb_begin + i) * TILE_K;
@@ -249,7 +257,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         // copies still in flight write into this CTA's shared memory: give them time to land
         for (int i = max(issued - STAGES, 0); i < issued; ++i) {
           const uint64_t start = now_ns();
-          while (!mbar_try(&full_bar[i % STAGES], (i / STAGES) & 1) && now_ns() - start < WAIT_LIMIT_NS) {}
+          while (!mbar_try(&full_bar[i % STAGES], (i / STAGES) & 1) && now_ns() - start < limit) {}
         }
       }
     }
@@ -259,7 +267,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       const uint32_t idesc = instr_desc(BM);
       for (int i = 0; i < n_kb; ++i) {
         const int s = i % STAGES;
-        if (!mbar_wait(&full_bar[s], (i / STAGES) & 1, abort)) break;
+        if (!mbar_wait(&full_bar[s], (i / STAGES) & 1, abort, limit)) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
         const uint64_t a_desc = smem_desc(a_addr), b_desc = smem_desc(a_addr + A_BYTES);
@@ -277,7 +285,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;                 // row of the tile = TMEM lane
     pdl_wait();   // before the first store: the output may be memory an earlier kernel still reads
-    const bool have = n_kb > 0 && mbar_wait(&acc_bar, 0, abort);
+    const bool have = n_kb > 0 && mbar_wait(&acc_bar, 0, abort, limit);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const int n = tile * TILE_N + r;                   // output column when not gated
 #pragma unroll 1
@@ -437,8 +445,9 @@ extern "C" {
 // splits (1..8) the number of CTAs that share a tile's k range, stages (2..8) the depth of the ring;
 // stages * (16 KB + bm * 128 B) must hold the bm x 128 float tile and fit in shared memory.
 // Returns -2 for sizes it does not take, -3/-4 if the tensor maps cannot be made.
-int sb_gemm_tcgen05(const void* x, const void* w, void* out, int rows, int n_out, int k_dim, int bm,
-                    int splits, int stages, int gated, int out_float, int* status, cudaStream_t s) {
+static int gemm_entry(const void* x, const void* w, void* out, int rows, int n_out, int k_dim, int bm,
+                      int splits, int stages, int gated, int out_float, int* status,
+                      unsigned long long wait_limit_ns, int withhold_stage, cudaStream_t s) {
   if (rows == 0 || n_out == 0) return 0;
   if (k_dim % 8 || k_dim <= 0 || splits < 1 || splits > GEMM_MAX_SPLITS) return -2;
   if (stages < 2 || stages > GEMM_MAX_STAGES) return -2;
@@ -456,6 +465,7 @@ int sb_gemm_tcgen05(const void* x, const void* w, void* out, int rows, int n_out
   args.out = out; args.status = status;
   args.rows = rows; args.n_out = n_out; args.k_dim = k_dim;
   args.splits = splits; args.stages = stages; args.gated = gated; args.out_float = out_float;
+  args.wait_limit_ns = wait_limit_ns; args.withhold_stage = withhold_stage;
 #define BY_TILE(G)                                                           \
   switch (bm) {                                                              \
     case 16: return launch<16, G>(map_w, map_x, args, tiles, m_tiles, s);    \
@@ -470,6 +480,23 @@ int sb_gemm_tcgen05(const void* x, const void* w, void* out, int rows, int n_out
   if (gated) { BY_TILE(true) }
   BY_TILE(false)
 #undef BY_TILE
+}
+
+int sb_gemm_tcgen05(const void* x, const void* w, void* out, int rows, int n_out, int k_dim, int bm,
+                    int splits, int stages, int gated, int out_float, int* status, cudaStream_t s) {
+  return gemm_entry(x, w, out, rows, n_out, k_dim, bm, splits, stages, gated, out_float, status,
+                    WAIT_LIMIT_NS, -1, s);
+}
+
+// The same product with one activation copy left out on purpose (k-block `withhold_stage` of every
+// CTA, which must be below `stages`) and waits that give up after `wait_limit_ns`: the kernel cannot
+// finish the product and must return with bit 4 of *status set.  The output is then undefined.
+int sb_gemm_tcgen05_withheld(const void* x, const void* w, void* out, int rows, int n_out, int k_dim, int bm,
+                             int splits, int stages, int gated, int out_float, int* status,
+                             unsigned long long wait_limit_ns, int withhold_stage, cudaStream_t s) {
+  if (withhold_stage < 0 || withhold_stage >= stages || wait_limit_ns == 0) return -2;
+  return gemm_entry(x, w, out, rows, n_out, k_dim, bm, splits, stages, gated, out_float, status,
+                    wait_limit_ns, withhold_stage, s);
 }
 
 }  // extern "C"

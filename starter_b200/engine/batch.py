@@ -18,6 +18,10 @@ import torch
 
 QUERY_TILE = 64
 
+#: in place of a token id in a ``StepEntry``: "the token the device drew for this sequence in the step
+#: before" (a captured single-token step can go on from it before the host has seen it)
+FED = None
+
 
 @dataclass
 class StepEntry:
@@ -47,6 +51,10 @@ class StepContext:
     max_kv_len: int
     cache: object
     status: torch.Tensor
+    #: the same arrays as numpy on the host, for parts that plan per sequence.  ``None`` in a captured
+    #: (CUDA-graph) step: nothing of the host may steer it, so a part that wants to run there works
+    #: from the device arrays above alone (every sequence then brings exactly one token, row ``i``
+    #: belongs to ``seq_slot[i]``)
     host: dict
 
     @property

@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import torch
 
+from ..cache.layout import PAGE_TOKENS
 from ..sampling.sampler import Sampler, SamplingParams
 from .generate import Completion, GenerationLoop, Request, pages_held
 from .runner import ModelRunner, load_model
@@ -22,7 +23,7 @@ class Engine:
     def __init__(self, model_path: str, dtype: str = "bfloat16", max_batch: int = 64,
                  max_tokens: int | None = None, device: str = "cuda:0") -> None:
         """Load the model in ``model_path`` (``config.json`` + safetensors).  ``max_tokens`` sizes the
-        cache (tokens over all live sequences, in pages of 64); by default it is sized by the first
+        cache (tokens over all live sequences, in cache pages); by default it is sized by the first
         call that needs it and grown by a later call that needs more."""
         self.model = load_model(model_path, dtype, device)
         self.max_batch = max_batch
@@ -53,13 +54,13 @@ class Engine:
 
     def _ensure_room(self, requests, batch: int) -> GenerationLoop:
         pages = sorted((pages_held(r) for r in requests), reverse=True)
-        need = sum(pages[:batch]) * 64
+        need = sum(pages[:batch]) * PAGE_TOKENS
         cache = self.runner.cache if self.runner is not None else None
         small = cache is not None and self._fixed_tokens is None and (
-            need > cache.num_pages * 64 or pages[0] > cache.max_pages_per_sequence)
+            need > cache.num_pages * PAGE_TOKENS or pages[0] > cache.max_pages_per_sequence)
         if cache is None or small:
             print(f"[engine] building the cache for {need} tokens", flush=True)
-            self._build_runner(max(need, 64), None if self._fixed_tokens else pages[0] * 64)
+            self._build_runner(max(need, PAGE_TOKENS), None if self._fixed_tokens else pages[0] * PAGE_TOKENS)
         return GenerationLoop(self.runner, self.sampler, batch, self.runner.cache.num_pages)
 
     # ------------------------------------------------------------------ the reference's call

@@ -19,10 +19,9 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
+from ..cache.layout import PAGE_TOKENS, pages_for
 from ..sampling.sampler import SamplingParams, request_key
-from .batch import StepEntry
-
-PAGE = 64
+from .batch import FED, StepEntry
 
 
 @dataclass
@@ -47,13 +46,25 @@ class Completion:
     finish_reason: str  # "stop" (a stop token was drawn; it is the last token) or "length"
 
 
+class _Ready:
+    """The handle of a step whose tokens are already on the host."""
+
+    device_feeds = False      # the device does not hold the next inputs: they go in from the host
+
+    def __init__(self, drawn):
+        self._drawn = list(drawn)
+
+    def result(self) -> list:
+        return self._drawn
+
+
 def tokens_held(request: Request) -> int:
     """Cache tokens a request can come to hold: the last drawn token is never fed back."""
     return len(request.prompt) + max(request.max_new_tokens - 1, 0)
 
 
 def pages_held(request: Request) -> int:
-    return (tokens_held(request) + PAGE - 1) // PAGE
+    return pages_for(tokens_held(request))
 
 
 def plan_batches(requests, max_batch: int, max_pages: int) -> list:
@@ -67,7 +78,7 @@ def plan_batches(requests, max_batch: int, max_pages: int) -> list:
             continue
         need = pages_held(req)
         if need > max_pages:
-            raise ValueError(f"request {i} needs {need} pages of {PAGE} tokens; the cache has {max_pages}")
+            raise ValueError(f"request {i} needs {need} pages of {PAGE_TOKENS} tokens; the cache has {max_pages}")
         if current and (len(current) == max_batch or used + need > max_pages):
             batches.append(current)
             current, used = [], 0
@@ -79,11 +90,30 @@ def plan_batches(requests, max_batch: int, max_pages: int) -> list:
 
 
 class GenerationLoop:
-    def __init__(self, runner, sampler, max_batch: int, max_pages: int):
+    def __init__(self, runner, sampler, max_batch: int, max_pages: int, lookahead: bool = True):
         self.runner = runner
         self.sampler = sampler
         self.max_batch = max_batch
         self.max_pages = max_pages
+        #: launch a step before the step before it has handed its tokens to the host, where that is
+        #: possible (see ``stream_batch``); the tokens are the same either way
+        self.lookahead = lookahead
+
+    def _start(self, entries, requests, active, keys, lengths):
+        """Launch one step for the ``active`` requests; returns a handle with ``result()``."""
+        runner = self.runner
+        temps = [requests[i].sampling.temperature for i in active]
+        now_keys = [keys[i] for i in active]
+        places = [lengths[i] for i in active]
+        if hasattr(runner, "start_step"):
+            return runner.start_step(entries, self.sampler, temps, now_keys, places)
+        if hasattr(runner, "step_and_select"):
+            drawn = runner.step_and_select(entries, self.sampler, temps, now_keys, places)
+        else:
+            drawn = self.sampler.select(runner.step(entries), temps, now_keys, places)
+        if hasattr(drawn, "tolist"):
+            drawn = drawn.tolist()        # one copy from the device, not one per sequence
+        return _Ready(drawn)
 
     def stream_batch(self, requests, numbers=None):
         """Run one batch; after every step yield ``{position in requests: token}`` for the sequences
@@ -107,16 +137,23 @@ class GenerationLoop:
             lengths = {i: len(requests[i].prompt) for i in active}
             entries = [StepEntry(slots[i], list(requests[i].prompt), [len(requests[i].prompt) - 1])
                        for i in active]
+            handle = self._start(entries, requests, active, keys, lengths)
             while active:
-                temps = [requests[i].sampling.temperature for i in active]
-                now_keys = [keys[i] for i in active]
-                places = [lengths[i] for i in active]
-                if hasattr(runner, "step_and_select"):
-                    drawn = runner.step_and_select(entries, self.sampler, temps, now_keys, places)
-                else:
-                    drawn = self.sampler.select(runner.step(entries), temps, now_keys, places)
-                if hasattr(drawn, "tolist"):
-                    drawn = drawn.tolist()        # one copy from the device, not one per sequence
+                # One step of lookahead (engine/engine.py:1081-1099).  Who is in the next step is
+                # known before this step's tokens are whenever no live request can stop on a token
+                # and none reaches its length now; the device holds the tokens it drew, so the next
+                # step is launched first and this step's tokens are read while it runs.
+                ahead = None
+                if self.lookahead and getattr(handle, "device_feeds", False) and all(
+                        not requests[i].stop_token_ids and len(outputs[i]) + 2 <= requests[i].max_new_tokens
+                        for i in active):
+                    for i in active:
+                        lengths[i] += 1
+                    ahead = self._start([StepEntry(slots[i], [FED], [0]) for i in active],
+                                        requests, active, keys, lengths)
+                    for i in active:
+                        lengths[i] -= 1
+                drawn = handle.result()
                 step_out = {}
                 still = []
                 for i, tok in zip(active, drawn):
@@ -134,7 +171,11 @@ class GenerationLoop:
                         runner.close_sequence(slots.pop(i))
                 yield step_out
                 active = still
-                entries = [StepEntry(slots[i], [outputs[i][-1]], [0]) for i in active]
+                if ahead is not None:
+                    handle = ahead
+                elif active:
+                    handle = self._start([StepEntry(slots[i], [outputs[i][-1]], [0]) for i in active],
+                                         requests, active, keys, lengths)
         finally:
             for slot in slots.values():
                 runner.close_sequence(slot)

@@ -17,6 +17,9 @@ sequence's keys into parts is decided at capture, from the class's shortest leng
 
 from __future__ import annotations
 
+import gc
+import weakref
+
 import numpy as np
 import torch
 
@@ -26,7 +29,11 @@ from .batch import StepContext
 
 class DecodeGraphs:
     def __init__(self, runner, max_batch: int):
-        self.runner = runner
+        # the runner owns this object; a weak reference back keeps the pair out of the cycle
+        # collector's hands, so that their pinned buffers are freed when the runner is dropped and
+        # not at some later moment of the collector's choosing (for instance in the middle of a
+        # stream capture, where freeing pinned memory that a stream has used is not allowed)
+        self._runner = weakref.ref(runner)
         self.max_batch = max_batch
         dev = runner.device
         # one int32 buffer holds every per-row field, so one copy refreshes a batch
@@ -44,11 +51,25 @@ class DecodeGraphs:
         self._stage_done = [None, None]
         self._views = {}
         self._stage_next = 0
+        # drawn tokens travel to the host through two pinned buffers in turn, so that the next step
+        # can be launched before the host has looked at this one's tokens (engine/engine.py:1081-1099)
+        self._out_host = [torch.zeros((max_batch,), dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._out_done = [torch.cuda.Event(), torch.cuda.Event()]
+        self._out_next = 0
         self.graphs = {}
-        self.logits = {}
+        self.logits = {}   # per graph, the float32 logits [batch, vocab] its last replay left
+        self.last_key = None  # the graph that ran last
         self.kernels_per_replay = {}  # this library's kernels inside each graph
         self.fed = None  # the slots whose next inputs the device already holds
+        self.fed_lengths = None  # and the lengths (tokens in the cache) the device holds them at
         self.kv_hint = 0  # the length the graph being captured is sized for (splits of the attention)
+
+    @property
+    def runner(self):
+        runner = self._runner()
+        if runner is None:
+            raise RuntimeError("the runner these graphs belong to is gone")
+        return runner
 
     def _field(self, name, batch):
         return self.meta[self.fields.index(name), :batch]
@@ -82,14 +103,29 @@ class DecodeGraphs:
         self.kernels_per_replay.clear()
 
     def _capture(self, batch: int, key) -> None:
+        # nothing may be freed behind the capture's back: collect what is collectable now and keep
+        # the cycle collector out until the graph is made
+        gc.collect()
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            self._capture_now(batch, key)
+        finally:
+            if collecting:
+                gc.enable()
+
+    def _capture_now(self, batch: int, key) -> None:
         # tables that grow with the sequence are sized for the longest sequence the cache can hold
         # before anything is captured, so that a long generation does not move them mid-way
         cache = self.runner.cache
-        self.runner.model.prepare(cache.max_pages_per_sequence * 64)
+        self.runner.model.prepare(cache.max_pages_per_sequence * ops.PAGE_TOKENS)
         saved = self.meta.clone()
         # warm up on a side stream (compiles kernels, sizes library workspaces), then capture;
-        # both run the real step, so the fields are restored afterwards and the cache rows the
-        # warm-up wrote are rewritten by the real step before they are ever read
+        # both run the real step on the live sequences.  What the step changes is put back
+        # afterwards: the fields, and the fixed-size state of every mixer that keeps one (a running
+        # sum would otherwise be advanced by the warm-up).  Keys and values need no care: the warm-up
+        # writes this step's own rows, which the real step writes again before they are ever read.
+        saved_state = {entry: tensor.clone() for entry, tensor in cache.state.items()}
         torch.cuda.synchronize()
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -100,6 +136,8 @@ class DecodeGraphs:
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         self.meta.copy_(saved)
+        for entry, tensor in saved_state.items():
+            cache.state[entry].copy_(tensor)
         graph = torch.cuda.CUDAGraph()
         before = ops.launch_count
         with torch.cuda.graph(graph):
@@ -107,10 +145,13 @@ class DecodeGraphs:
         self.kernels_per_replay[batch] = ops.launch_count - before
         self.graphs[key] = graph
         self.meta.copy_(saved)
+        for entry, tensor in saved_state.items():
+            cache.state[entry].copy_(tensor)
         torch.cuda.synchronize()
 
     def load(self, slots, tokens, positions, temperatures, keys) -> None:
-        """Put a batch's rows on the device (one copy)."""
+        """Put a batch's rows on the device (one copy).  ``tokens`` None: the device keeps the tokens
+        it drew itself and only the fields the host owns are refreshed."""
         batch = len(slots)
         turn = self._stage_next
         self._stage_next = 1 - turn
@@ -120,18 +161,22 @@ class DecodeGraphs:
         else:
             done.synchronize()            # the copy that last read this buffer has long finished
         host = self._stage_np[turn]
-        host[0, :batch] = tokens
+        first = 0 if tokens is not None else 1
+        if tokens is not None:
+            host[0, :batch] = tokens
         host[1, :batch] = positions
         host[2, :batch] = slots
         host[3, :batch] = host[1, :batch] + 1
         self._stage_f32[turn][4, :batch] = temperatures
         self._stage_u32[turn][5, :batch] = keys
-        views = self._views.get((turn, batch))
+        views = self._views.get((turn, batch, first))
         if views is None:
-            views = self._views[(turn, batch)] = (self.meta[:, :batch], self._stage[turn][:, :batch])
+            views = self._views[(turn, batch, first)] = (self.meta[first:, :batch],
+                                                          self._stage[turn][first:, :batch])
         views[0].copy_(views[1], non_blocking=True)
         done.record()
         self.fed = tuple(slots)
+        self.fed_lengths = list(positions)
 
     def replay(self, batch: int, kv_tokens: int = 0) -> torch.Tensor:
         """Run one step for the ``batch`` rows on the device; returns the drawn tokens (device).
@@ -146,7 +191,32 @@ class DecodeGraphs:
             self.kv_hint = pages * ops.PAGE_TOKENS
             self._capture(batch, key)
         self.graphs[key].replay()
+        self.last_key = key
         return self.out[:batch]
+
+    def fetch(self, batch: int) -> DrawnTokens:
+        """Start the copy of the last replay's tokens to pinned host memory; nothing waits here."""
+        turn = self._out_next
+        self._out_next = 1 - turn
+        self._out_host[turn][:batch].copy_(self.out[:batch], non_blocking=True)
+        self._out_done[turn].record()
+        return DrawnTokens(self._out_host[turn], self._out_done[turn], batch)
+
+
+class DrawnTokens:
+    """The tokens of a step that is (or was) running: ``result()`` waits for them and returns a list."""
+
+    def __init__(self, host=None, done=None, batch=0, ready=None):
+        self._host, self._done, self._batch, self._ready = host, done, batch, ready
+        #: True if the device also kept these tokens as the sequences' next inputs, so that the next
+        #: step can be launched without them
+        self.device_feeds = ready is None
+
+    def result(self) -> list:
+        if self._ready is None:
+            self._done.synchronize()
+            self._ready = self._host[:self._batch].tolist()
+        return self._ready
 
 
 #: length classes of the captured decode graphs, in cache pages: powers of two and their 1.5-folds

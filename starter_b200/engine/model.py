@@ -16,21 +16,33 @@ from ..parts import ParamSpec, lookup
 
 
 def build_layers(spec, dtype, device):
-    """Instantiate every layer's parts; position parts with equal specs are shared."""
+    """Instantiate every layer's parts; position parts with equal specs are shared.
+
+    The layer's arrangement names the parts it is made of and their families; each part's spec is
+    looked up under that family by its ``kind``.  A part whose spec carries a ``position`` spec is
+    handed the position part built from it."""
     positions = {}
     blocks = []
-    for layer in spec.layers:
-        pos_spec = getattr(layer.mixer, "position", None)
-        position = None
-        if pos_spec is not None:
-            if pos_spec not in positions:
+    for index, layer in enumerate(spec.layers):
+        arrangement = lookup("arrangement", layer.arrangement)
+        wanted = dict(arrangement.FAMILIES)
+        missing = [n for n in wanted if n not in layer.parts]
+        extra = [n for n in layer.parts if n not in wanted]
+        if missing or extra:
+            raise ValueError(f"layer {index}: the {layer.arrangement!r} arrangement is made of "
+                             f"{sorted(wanted)}; the layer spec lacks {missing} and has {extra} besides")
+        built = {}
+        for name, family in wanted.items():
+            part_spec = layer.parts[name]
+            cls = lookup(family, part_spec.kind)
+            pos_spec = getattr(part_spec, "position", None)
+            if pos_spec is not None and pos_spec not in positions:
                 positions[pos_spec] = lookup("position", pos_spec.kind)(pos_spec, dtype, device)
-            position = positions[pos_spec]
-        mixer = lookup("mixer", layer.mixer.kind)(layer.mixer, dtype, position)
-        feed_forward = lookup("feed_forward", layer.feed_forward.kind)(layer.feed_forward, dtype)
-        norm1 = lookup("norm", layer.norm1.kind)(layer.norm1, dtype)
-        norm2 = lookup("norm", layer.norm2.kind)(layer.norm2, dtype)
-        blocks.append(lookup("arrangement", layer.arrangement)(mixer, feed_forward, norm1, norm2))
+            if family == "mixer":
+                built[name] = cls(part_spec, dtype, positions.get(pos_spec))
+            else:
+                built[name] = cls(part_spec, dtype)
+        blocks.append(arrangement(built))
     return blocks, list(positions.values())
 
 
@@ -84,19 +96,26 @@ class DecoderModel:
     def expected_tensors(self) -> dict:
         return expected_tensors(self.spec)
 
-    def load_tensors(self, tensors: dict) -> None:
-        """Take ``{checkpoint name: device tensor}`` (already placed by the loader)."""
+    def load_tensors(self, tensors) -> None:
+        """Take a mapping ``checkpoint name -> device tensor`` (a dict, or the loader's mapping that
+        places a tensor when it is asked for).  Layers are taken one at a time and a layer's tensors
+        are let go of as soon as its parts have them (stacked where a part stacks), so loading never
+        holds two copies of more than one layer."""
         spec = self.spec
         self.embed = tensors[spec.embed_name]
         self.lm_head = self.embed if spec.tie_embeddings else tensors[spec.lm_head_name]
         self.final_norm.set_params({"weight": tensors[spec.final_norm_name]})
         for block, layer in zip(self.blocks, spec.layers):
             grouped = {}
-            for name, (part_name, logical, _) in _layer_params(block, layer.names).items():
+            wanted = _layer_params(block, layer.names)
+            for name, (part_name, logical, _) in wanted.items():
                 grouped.setdefault(part_name, {})[logical] = tensors[name]
             for part_name, part in block.parts().items():
                 if part.param_specs():
                     part.set_params(grouped[part_name])
+            del grouped
+            for name in wanted:
+                tensors.pop(name, None)
 
     # ------------------------------------------------------------------ cache needs
 
@@ -122,7 +141,10 @@ class DecoderModel:
         any device table moved: graphs captured before then hold stale addresses."""
         moved = False
         for block in self.blocks:
-            moved = bool(block.mixer.prepare(max_position)) or moved
+            for part in block.parts().values():
+                prepare = getattr(part, "prepare", None)
+                if prepare is not None:
+                    moved = bool(prepare(max_position)) or moved
         return moved
 
     def hidden(self, ctx):
@@ -134,16 +156,16 @@ class DecoderModel:
                                                          entry.writes_cache)
         return residual, pending
 
-    def logits(self, residual, pending, rows):
+    def logits(self, residual, pending, rows, status=None):
         """Float32 logits ``[len(rows), vocab]`` of the rows asked for."""
         h = self.final_norm.add_rows(residual, pending, rows)
-        return ops.linear(h, self.lm_head, out_float=True)
+        return ops.linear(h, self.lm_head, out_float=True, status=status)
 
     def forward(self, ctx, rows):
         residual, pending = self.hidden(ctx)
         if rows is None or rows.numel() == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
-        return self.logits(residual, pending, rows)
+        return self.logits(residual, pending, rows, ctx.status)
 
     def step_weight_bytes(self) -> int:
         """Bytes of weights one decode step reads: every layer the run order names, each time it is

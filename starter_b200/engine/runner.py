@@ -16,11 +16,11 @@ import os
 
 import torch
 
-from ..cache import SequenceCache
+from ..cache import SequenceCache, pages_for
 from ..config import load_config
 from ..weights import load_checkpoint
-from .batch import StepContext, StepEntry, plan_step, upload
-from .graphs import DecodeGraphs
+from .batch import FED, StepContext, StepEntry, plan_step, upload
+from .graphs import DecodeGraphs, DrawnTokens
 from .model import DecoderModel
 
 DTYPES = {
@@ -87,24 +87,34 @@ class ModelRunner:
                  max_sequence_tokens: int | None = None, use_graphs: bool = True):
         self.model = model
         self.device = model.device
-        pages = (max_tokens + 63) // 64
+        pages = pages_for(max_tokens)
         if max_sequences is None:
             max_sequences = min(pages, 1024)
         self.cache = SequenceCache(model.kv_needs(), model.state_needs(), max_tokens, max_sequences,
                                    model.dtype, self.device, max_sequence_tokens)
         self.status = torch.zeros((1,), dtype=torch.int32, device=self.device)
         self.graphs = DecodeGraphs(self, max_sequences) if use_graphs else None
-        #: with False, every one-token step takes its tokens from the host (one small copy per step)
-        #: instead of from the token the device drew in the step before
+        #: with False, every one-token step gets its inputs from pinned host memory (one small copy
+        #: per step: positions, slots, lengths, sampling settings, and the tokens too when the host
+        #: has them) instead of going on from what the device holds
         self.self_feeding = True
 
     # ------------------------------------------------------------------ sequences
 
     def open_sequence(self) -> int:
-        return self.cache.open_sequence()
+        slot = self.cache.open_sequence()
+        self._forget_fed(slot)
+        return slot
 
     def close_sequence(self, slot: int) -> None:
         self.cache.close_sequence(slot)
+        self._forget_fed(slot)
+
+    def _forget_fed(self, slot: int) -> None:
+        """What the device holds as the next input of ``slot`` belongs to a sequence that is gone."""
+        graphs = self.graphs
+        if graphs is not None and graphs.fed is not None and slot in graphs.fed:
+            graphs.fed = None
 
     def reserve(self, slot: int, tokens: int) -> None:
         """Set pages aside so that ``slot`` can grow to ``tokens`` tokens without asking again."""
@@ -119,10 +129,10 @@ class ModelRunner:
 
     def make_context(self, entries) -> StepContext:
         cache = self.cache
-        for e in entries:
-            cache.reserve(e.slot, cache.lengths[e.slot] + len(e.tokens))
         starts = [cache.lengths[e.slot] for e in entries]
         arrays = plan_step(entries, starts, self.model.spec.vocab_size)
+        for e in entries:
+            cache.reserve(e.slot, cache.lengths[e.slot] + len(e.tokens))
         for e in entries:
             cache.advance(e.slot, len(e.tokens))
         cache.sync_table()
@@ -144,8 +154,18 @@ class ModelRunner:
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         if self.graphs is not None:
             self.graphs.fed = None
-        ctx = self.make_context(entries)
-        return self.model.forward(ctx, ctx.want_rows)
+        cache = self.cache
+        before = [(e.slot, cache.lengths[e.slot]) for e in entries]
+        try:
+            ctx = self.make_context(entries)
+            return self.model.forward(ctx, ctx.want_rows)
+        except BaseException:
+            # a step that raises leaves every sequence as long as it was: tokens whose keys were
+            # never (or only partly) written are not counted, and later steps do not read them
+            for slot, length in before:
+                if cache.slots.is_held(slot):
+                    cache.lengths[slot] = length
+            raise
 
     @torch.inference_mode()
     def step_and_select(self, entries, sampler, temperatures, keys, positions) -> list:
@@ -153,10 +173,21 @@ class ModelRunner:
 
         Steps in which every sequence brings one token run as a captured graph that feeds itself;
         anything else runs the eager step and the sampler.  Both run the same kernels."""
+        return self.start_step(entries, sampler, temperatures, keys, positions).result()
+
+    @torch.inference_mode()
+    def start_step(self, entries, sampler, temperatures, keys, positions) -> DrawnTokens:
+        """``step_and_select`` without the wait: launches the step and returns a handle whose
+        ``result()`` gives the drawn tokens.  An entry whose token is ``FED`` goes on from the token the
+        device drew for it in the step before, which the host need not have seen yet; that is what
+        lets a step be launched before its predecessor's tokens are read."""
         single = self.graphs is not None and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
         if not single:
-            return sampler.select(self.step(entries), temperatures, keys, positions)
-        return self.decode_tokens(entries, temperatures, keys).tolist()
+            if any(t is FED for e in entries for t in e.tokens):
+                raise ValueError("only a captured single-token step can go on from device-held tokens")
+            return DrawnTokens(ready=sampler.select(self.step(entries), temperatures, keys, positions))
+        self.decode_tokens(entries, temperatures, keys)
+        return self.graphs.fetch(len(entries))
 
     @torch.inference_mode()
     def decode_tokens(self, entries, temperatures, keys) -> torch.Tensor:
@@ -165,18 +196,30 @@ class ModelRunner:
         slots = tuple(e.slot for e in entries)
         for e in entries:
             cache.reserve(e.slot, cache.lengths[e.slot] + 1)
-        if graphs.fed != slots or not self.self_feeding:
+        lengths = [cache.lengths[s] for s in slots]
+        # the device may go on from what it drew itself only for the very same sequences at the
+        # very lengths it left them at; anything else (another batch, a slot that was closed and
+        # opened again, a step that came in between) is loaded from the host
+        held = graphs.fed == slots and graphs.fed_lengths == lengths
+        unknown = any(e.tokens[0] is FED for e in entries)
+        if unknown and not held:
+            raise RuntimeError("a step asked to go on from device-held tokens, but the device does not "
+                               "hold the next inputs of exactly these sequences")
+        if unknown and not self.self_feeding:
+            graphs.load(slots, None, lengths, temperatures, keys)     # all but the tokens from the host
+        elif not held or not self.self_feeding:
             for e in entries:
                 if not 0 <= e.tokens[0] < self.model.spec.vocab_size:
                     raise ValueError(f"token id {e.tokens[0]} is outside the vocabulary")
-            graphs.load(slots, [e.tokens[0] for e in entries], [cache.lengths[s] for s in slots],
-                        temperatures, keys)
+            graphs.load(slots, [e.tokens[0] for e in entries], lengths, temperatures, keys)
+        cache.sync_table()
+        longest = max(lengths) + 1
+        self.prepare(longest)
+        out = graphs.replay(len(slots), longest)
         for s in slots:
             cache.advance(s, 1)
-        cache.sync_table()
-        longest = max(cache.lengths[s] for s in slots)
-        self.prepare(longest)
-        return graphs.replay(len(slots), longest)
+        graphs.fed_lengths = [n + 1 for n in lengths]
+        return out
 
     def check_status(self) -> None:
         """Raise if a kernel flagged a bad input since the last check (reads one int from the device)."""

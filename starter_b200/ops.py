@@ -13,9 +13,9 @@ import ctypes
 
 import torch
 
+from .cache.layout import PAGE_TOKENS
 from .csrc import build
 
-PAGE_TOKENS = 64
 SMALL_ROWS = 16
 #: Up to this many rows the bfloat16 product runs on this library's tcgen05 kernel, where it is bound
 #: by streaming the weights; beyond it (prompts) the vendor's GEMM is used, as the reference does
@@ -29,6 +29,21 @@ _DT = {torch.float32: 0, torch.bfloat16: 1}
 
 class KernelError(RuntimeError):
     pass
+
+
+_checked = set()
+
+
+def _lib(name: str):
+    """The kernel library of ``name.cu``; refuses one compiled for another cache page size."""
+    lib = build.load(name)
+    if name not in _checked:
+        compiled = lib.sb_page_tokens()
+        if compiled != PAGE_TOKENS:
+            raise KernelError(f"libsb_{name} was compiled for cache pages of {compiled} tokens, the cache "
+                              f"uses pages of {PAGE_TOKENS}")
+        _checked.add(name)
+    return lib
 
 
 def _code(dtype) -> int:
@@ -86,7 +101,7 @@ def embedding(tokens, table, status=None):
     _need(tokens, "tokens", torch.int32, 1)
     _need(table, "table", None, 2)
     out = torch.empty((tokens.shape[0], table.shape[1]), dtype=table.dtype, device=table.device)
-    rc = build.load("elementwise").sb_embedding(
+    rc = _lib("elementwise").sb_embedding(
         _code(table.dtype), _ptr(tokens), _ptr(table), _ptr(out), tokens.shape[0], table.shape[1],
         table.shape[0], _ptr(status), _stream())
     _check(rc, "embedding")
@@ -115,7 +130,7 @@ def rmsnorm(x, gain, eps, delta=None, rows=None, out=None):
         n_rows = rows.shape[0]
     if out is None:
         out = torch.empty((n_rows, hidden), dtype=x.dtype, device=x.device)
-    rc = build.load("elementwise").sb_rmsnorm(
+    rc = _lib("elementwise").sb_rmsnorm(
         _code(x.dtype), _gain_code(x, gain), _ptr(x), _ptr(delta), _ptr(gain), _ptr(out), _ptr(rows),
         n_rows, hidden, ctypes.c_float(eps), _stream())
     _check(rc, "rmsnorm")
@@ -129,7 +144,7 @@ def swiglu(gate_up):
         raise KernelError(f"gate_up has an odd width {gate_up.shape[1]}")
     inner = gate_up.shape[1] // 2
     out = torch.empty((gate_up.shape[0], inner), dtype=gate_up.dtype, device=gate_up.device)
-    rc = build.load("elementwise").sb_swiglu(
+    rc = _lib("elementwise").sb_swiglu(
         _code(gate_up.dtype), _ptr(gate_up), _ptr(out), gate_up.shape[0], inner, _stream())
     _check(rc, "swiglu")
     return out
@@ -137,12 +152,13 @@ def swiglu(gate_up):
 
 # ---------------------------------------------------------------------------------------- matrix products
 
-def linear(x, weight, out_float=False, gated=False):
+def linear(x, weight, out_float=False, gated=False, status=None):
     """``x @ weight.T`` for ``x`` ``[T, K]`` and ``weight`` ``[N, K]`` (no bias).
 
     ``gated``: ``weight`` is ``[gate; up]`` stacked (``[2 * I, K]``) and the result is
     ``round(silu(x @ gate.T)) * (x @ up.T)`` of shape ``[T, I]``.  ``out_float``
-    returns float32 whatever the working type (used for logits).
+    returns float32 whatever the working type (used for logits).  ``status`` (int32 ``[1]``) is the
+    device word in which the tensor-core kernel reports a wait that ran out.
     """
     _need(x, "x", None, 2)
     _need(weight, "weight", x.dtype, 2)
@@ -155,20 +171,20 @@ def linear(x, weight, out_float=False, gated=False):
     n_out = n_total // 2 if gated else n_total
     dt = _code(x.dtype)
     if dt == 1 and rows <= TENSOR_CORE_MAX_ROWS and tensor_core_ok(x, weight, gated, n_out):
-        return linear_tensor_core(x, weight, out_float=out_float, gated=gated)
+        return linear_tensor_core(x, weight, out_float=out_float, gated=gated, status=status)
     if rows <= SMALL_ROWS:
         out_dtype = torch.float32 if (out_float or dt == 0) else x.dtype
         if gated and out_float and dt == 1:
             raise KernelError("a gated product cannot return float32 from bfloat16")
         y = torch.empty((rows, n_out), dtype=out_dtype, device=x.device)
-        rc = build.load("linear_small").sb_linear_small(
+        rc = _lib("linear_small").sb_linear_small(
             dt, int(out_float), int(gated), _ptr(x), _ptr(weight), _ptr(y), rows, n_out, k_dim,
             _stream())
         _check(rc, "linear_small")
         return y
     if dt == 0:
         y = torch.empty((rows, n_total), dtype=torch.float32, device=x.device)
-        rc = build.load("sgemm").sb_sgemm_nt(_ptr(x), _ptr(weight), _ptr(y), rows, n_total, k_dim,
+        rc = _lib("sgemm").sb_sgemm_nt(_ptr(x), _ptr(weight), _ptr(y), rows, n_total, k_dim,
                                              _stream())
         _check(rc, "sgemm")
     elif out_float:
@@ -222,8 +238,12 @@ def gemm_plan(rows: int, n_out: int, k_dim: int, gated: bool):
 
 
 def linear_tensor_core(x, weight, out_float=False, gated=False, bm=None, splits=None, stages=None,
-                       status=None):
-    """The bfloat16 product on tcgen05 tensor cores (csrc/gemm_tcgen05.cu)."""
+                       status=None, withhold=None):
+    """The bfloat16 product on tcgen05 tensor cores (csrc/gemm_tcgen05.cu).
+
+    ``withhold = (k_block, limit_ns)`` is for tests of the kernel's give-up path: the activation copy
+    of that k-block is left out, so a wait inside the kernel runs out after ``limit_ns``; the kernel
+    returns, bit 4 of ``status`` is set and the result is undefined."""
     _need(x, "x", torch.bfloat16, 2)
     _need(weight, "weight", torch.bfloat16, 2)
     rows, k_dim = x.shape
@@ -239,9 +259,14 @@ def linear_tensor_core(x, weight, out_float=False, gated=False, bm=None, splits=
     splits = splits or plan[1]
     stages = stages or max(plan[2], -(-bm * 512 // (16384 + bm * 128)))
     out = torch.empty((rows, n_out), dtype=torch.float32 if out_float else torch.bfloat16, device=x.device)
-    rc = build.load("gemm_tcgen05").sb_gemm_tcgen05(
-        _ptr(x), _ptr(weight), _ptr(out), rows, n_out, k_dim, bm, splits, stages, int(gated),
-        int(out_float), _ptr(status), _stream())
+    if withhold is not None:
+        rc = _lib("gemm_tcgen05").sb_gemm_tcgen05_withheld(
+            _ptr(x), _ptr(weight), _ptr(out), rows, n_out, k_dim, bm, splits, stages, int(gated),
+            int(out_float), _ptr(status), ctypes.c_ulonglong(int(withhold[1])), int(withhold[0]), _stream())
+    else:
+        rc = _lib("gemm_tcgen05").sb_gemm_tcgen05(
+            _ptr(x), _ptr(weight), _ptr(out), rows, n_out, k_dim, bm, splits, stages, int(gated),
+            int(out_float), _ptr(status), _stream())
     if rc in (-3, -4):
         raise KernelError("the TMA descriptors for the tensor-core product could not be made "
                           f"(code {rc}); is the driver too old for cuTensorMapEncodeTiled?")
@@ -250,6 +275,19 @@ def linear_tensor_core(x, weight, out_float=False, gated=False, bm=None, splits=
 
 
 # ---------------------------------------------------------------------------------------- attention
+
+def rotation_tables(rotation, head_dim: int):
+    """``(cos, sin)`` for the kernels from a position part's ``Rotation`` (or ``(None, None)``).
+
+    The kernels here (``qk_norm_rope_store`` and the decode attention that rotates the new token
+    itself) turn the whole head in half-split layout; anything else is refused by name."""
+    if rotation is None:
+        return None, None
+    if rotation.layout != "half_split" or rotation.rotary_dim != head_dim:
+        raise KernelError(f"the kernels rotate the whole head ({head_dim} dimensions) in half-split layout; "
+                          f"asked for {rotation.rotary_dim} dimensions in {rotation.layout!r} layout")
+    return rotation.cos, rotation.sin
+
 
 def qk_norm_rope_store(qkv, heads, kv_heads, head_dim, q_gain, k_gain, eps, cos_table, sin_table,
                        tok_pos, tok_slot, block_table, k_store, v_store, write_cache=True):
@@ -291,7 +329,7 @@ def qk_norm_rope_store(qkv, heads, kv_heads, head_dim, q_gain, k_gain, eps, cos_
                 raise KernelError(f"cache pages have shape {tuple(store.shape)}, expected "
                                   f"[pages, {kv_heads}, {PAGE_TOKENS}, {head_dim}]")
     q_out = torch.empty((n_tokens, heads * head_dim), dtype=qkv.dtype, device=qkv.device)
-    rc = build.load("rope_cache").sb_qk_norm_rope_store(
+    rc = _lib("rope_cache").sb_qk_norm_rope_store(
         _code(qkv.dtype), gain_code, _ptr(qkv), _ptr(q_out), _ptr(q_gain), _ptr(k_gain),
         _ptr(cos_table), _ptr(sin_table), _ptr(tok_pos), _ptr(tok_slot), _ptr(block_table),
         block_table.shape[1], _ptr(k_store if write_cache else None),
@@ -319,7 +357,7 @@ def attention_rowwise(q, k_store, v_store, block_table, tok_slot, tok_pos, heads
     _need(tok_slot, "tok_slot", torch.int32, 1)
     _need(tok_pos, "tok_pos", torch.int32, 1)
     out = torch.empty_like(q)
-    rc = build.load("attention_rowwise").sb_attention_rowwise(
+    rc = _lib("attention_rowwise").sb_attention_rowwise(
         _code(q.dtype), _ptr(q), _ptr(out), _ptr(k_store), _ptr(v_store), _ptr(block_table),
         block_table.shape[1], _ptr(tok_slot), _ptr(tok_pos), q.shape[0], heads, kv_heads, head_dim,
         ctypes.c_float(scale), int(window or 0), _stream())
@@ -364,7 +402,7 @@ def attention_prefill(q, k_store, v_store, block_table, seq_slot, seq_q_start, s
             raise KernelError(f"the tcgen05 prefill kernel takes head_dim {PREFILL_TC_HEAD_DIMS}, not {head_dim}")
         if not q.is_contiguous():
             raise KernelError("q must be contiguous")
-        rc = build.load("attention_prefill_tc").sb_attention_prefill_tc(
+        rc = _lib("attention_prefill_tc").sb_attention_prefill_tc(
             _ptr(q), _ptr(out), _ptr(k_store), _ptr(v_store), _ptr(block_table), block_table.shape[1],
             _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), _ptr(seq_kv_len), _ptr(tile_seq),
             _ptr(tile_first), tile_seq.shape[0], q.shape[0], k_store.shape[0], heads, kv_heads, head_dim,
@@ -372,7 +410,7 @@ def attention_prefill(q, k_store, v_store, block_table, seq_slot, seq_q_start, s
             _stream())
         _check(rc, "attention_prefill_tc")
         return out
-    rc = build.load("attention_prefill").sb_attention_prefill(
+    rc = _lib("attention_prefill").sb_attention_prefill(
         _ptr(q), _ptr(out), _ptr(k_store), _ptr(v_store), _ptr(block_table), block_table.shape[1],
         _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), _ptr(seq_kv_len), _ptr(tile_seq),
         _ptr(tile_first), tile_seq.shape[0], heads, kv_heads, head_dim, ctypes.c_float(scale),
@@ -463,7 +501,7 @@ def attention_decode_qkv(qkv, k_store, v_store, block_table, row_slot, row_kv_le
     if n_splits > 1 and not in_cluster:
         part_acc = torch.empty((rows * heads * n_splits * head_dim,), dtype=torch.float32, device=qkv.device)
         part_ml = torch.empty((rows * heads * n_splits * 2,), dtype=torch.float32, device=qkv.device)
-    rc = build.load("attention_decode_mma").sb_attention_decode_mma_fused(
+    rc = _lib("attention_decode_mma").sb_attention_decode_mma_fused(
         _ptr(qkv), qkv.shape[1], _ptr(out), _ptr(k_store), _ptr(v_store), _ptr(block_table),
         block_table.shape[1], _ptr(row_slot), _ptr(row_kv_len), rows, heads, kv_heads, head_dim,
         ctypes.c_float(scale), int(window or 0), n_splits, _ptr(part_acc), _ptr(part_ml), _ptr(q_gain),
@@ -507,12 +545,12 @@ def attention_decode(q, k_store, v_store, block_table, row_slot, row_kv_len, hea
         part_acc = torch.empty((rows * heads * n_splits * head_dim,), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((rows * heads * n_splits * 2,), dtype=torch.float32, device=q.device)
     if tensor_cores:
-        rc = build.load("attention_decode_mma").sb_attention_decode_mma(
+        rc = _lib("attention_decode_mma").sb_attention_decode_mma(
             _ptr(q), _ptr(out), _ptr(k_store), _ptr(v_store), _ptr(block_table), block_table.shape[1],
             _ptr(row_slot), _ptr(row_kv_len), rows, heads, kv_heads, head_dim, ctypes.c_float(scale),
             int(window or 0), n_splits, _ptr(part_acc), _ptr(part_ml), _stream())
     else:
-        rc = build.load("attention_decode").sb_attention_decode(
+        rc = _lib("attention_decode").sb_attention_decode(
             _code(q.dtype), _ptr(q), _ptr(out), _ptr(k_store), _ptr(v_store), _ptr(block_table),
             block_table.shape[1], _ptr(row_slot), _ptr(row_kv_len), rows, heads, kv_heads, head_dim,
             ctypes.c_float(scale), int(window or 0), n_splits, _ptr(part_acc), _ptr(part_ml),
@@ -536,7 +574,7 @@ def sample(logits, temperature=None, request_key=None, position=None, status=Non
         _need(position, "position", torch.int32, 1)
     if out is None:
         out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
-    lib = build.load("sampling")
+    lib = _lib("sampling")
     chunks = lib.sb_sample_chunks(vocab)
     cand_v = torch.empty((rows * chunks,), dtype=torch.float32, device=logits.device)
     cand_i = torch.empty((rows * chunks,), dtype=torch.int32, device=logits.device)

@@ -1,10 +1,10 @@
 from .attention import GroupedQueryAttention
-from .base import ParamSpec, Part
+from .base import ROLES, ParamSpec, Part, Role, register_role, role_of
 from .block import PreNormBlock
 from .feedforward import GatedFeedForward
 from .norm import RMSNorm
 from .registry import FAMILIES, lookup, register
-from .rotary import RotaryTable
+from .rotary import Rotation, RotaryTable
 
-__all__ = ["FAMILIES", "GatedFeedForward", "GroupedQueryAttention", "ParamSpec", "Part",
-           "PreNormBlock", "RMSNorm", "RotaryTable", "lookup", "register"]
+__all__ = ["FAMILIES", "ROLES", "Role", "register_role", "role_of", "GatedFeedForward", "GroupedQueryAttention", "ParamSpec", "Part",
+           "PreNormBlock", "RMSNorm", "RotaryTable", "Rotation", "lookup", "register"]

@@ -63,21 +63,30 @@ class GroupedQueryAttention(Part):
             return bool(self.position.ensure(max_position + 1))
         return False
 
+    def _rotation(self):
+        if self.position is None:
+            return None
+        rotation = getattr(self.position, "rotation", None)
+        if rotation is None:
+            raise ValueError(f"the position part {type(self.position).__name__} offers no rotation(); "
+                             "this attention takes rotary positions (or none)")
+        return rotation()
+
     def __call__(self, x, ctx, entry, writes_cache=True):
         s = self.spec
         cache = ctx.cache
         keys, values = cache.entry_pages(entry)
         weight = self.qkv if writes_cache else self.qkv[: self.q_size]
-        qkv = ops.linear(x, weight)
-        cos = self.position.cos if self.position is not None else None
-        sin = self.position.sin if self.position is not None else None
+        qkv = ops.linear(x, weight, status=ctx.status)
+        # the position part says what it turns and how; the kernels take or refuse it by name
+        cos, sin = ops.rotation_tables(self._rotation(), s.head_dim)
         if ctx.max_q_len == 1 and ops.decode_from_qkv_takes(s.head_dim, qkv.dtype):
             # one token per sequence: head norm, rotation and cache write inside the attention kernel
             a = ops.attention_decode_qkv(qkv, keys, values, cache.block_table, ctx.seq_slot, ctx.seq_kv_len,
                                          s.num_heads, s.num_kv_heads, s.head_dim, s.scale, s.window,
                                          self.q_norm, self.k_norm, s.qk_norm_eps, cos, sin,
                                          write_cache=writes_cache, kv_hint=ctx.max_kv_len)
-            return ops.linear(a, self.o)
+            return ops.linear(a, self.o, status=ctx.status)
         q = ops.qk_norm_rope_store(
             qkv, s.num_heads, s.num_kv_heads, s.head_dim, self.q_norm, self.k_norm, s.qk_norm_eps,
             cos, sin, ctx.tok_pos, ctx.tok_slot, cache.block_table, keys, values,
@@ -94,7 +103,7 @@ class GroupedQueryAttention(Part):
         else:
             a = ops.attention_rowwise(q, keys, values, cache.block_table, ctx.tok_slot, ctx.tok_pos,
                                       s.num_heads, s.num_kv_heads, s.head_dim, s.scale, s.window)
-        return ops.linear(a, self.o)
+        return ops.linear(a, self.o, status=ctx.status)
 
     def weight_bytes(self):
         return bytes_of(self.qkv, self.o, self.q_norm, self.k_norm)

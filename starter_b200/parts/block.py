@@ -6,21 +6,27 @@ the two are one kernel: a block takes ``(residual, pending)``, where ``pending``
 is the previous block's output not yet added, and returns the same pair
 (engine/engine.py:669-673).  The model's final norm closes the chain the same way.
 A block does not know its neighbours or the model it is in.
+
+An arrangement says which parts it is made of: ``FAMILIES`` maps each part's name inside the layer
+to the family its spec is looked up in.  The model builds exactly those parts from the layer spec
+and hands them over by name; ``mixer`` names the part that owns the layer's cache entry.
 """
 
 from __future__ import annotations
 
 
 class PreNormBlock:
-    def __init__(self, mixer, feed_forward, norm1, norm2):
-        self.mixer = mixer
-        self.feed_forward = feed_forward
-        self.norm1 = norm1
-        self.norm2 = norm2
+    FAMILIES = {"mixer": "mixer", "feed_forward": "feed_forward", "norm1": "norm", "norm2": "norm"}
+
+    def __init__(self, parts: dict):
+        self._parts = dict(parts)
+        self.mixer = parts["mixer"]
+        self.feed_forward = parts["feed_forward"]
+        self.norm1 = parts["norm1"]
+        self.norm2 = parts["norm2"]
 
     def parts(self) -> dict:
-        return {"mixer": self.mixer, "feed_forward": self.feed_forward,
-                "norm1": self.norm1, "norm2": self.norm2}
+        return dict(self._parts)
 
     def __call__(self, residual, pending, ctx, entry, writes_cache=True):
         n = self.norm1.add(residual, pending)

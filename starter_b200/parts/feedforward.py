@@ -26,8 +26,9 @@ class GatedFeedForward(Part):
         self.down = params["down"].contiguous()
 
     def __call__(self, x, ctx=None):
-        act = ops.linear(x, self.gate_up, gated=True)
-        return ops.linear(act, self.down)
+        status = ctx.status if ctx is not None else None
+        act = ops.linear(x, self.gate_up, gated=True, status=status)
+        return ops.linear(act, self.down, status=status)
 
     def weight_bytes(self):
         return bytes_of(self.gate_up, self.down)

@@ -11,8 +11,11 @@ Families and their interfaces
   feed_forward  ``__init__(spec, dtype)``; ``param_specs()``, ``set_params``, ``__call__(x, ctx)``
   norm          ``__init__(spec, dtype)``; ``param_specs()``, ``set_params``, ``__call__(x)``,
                 ``add(residual, delta)``, ``add_rows(residual, delta, rows)``
-  position      ``__init__(spec, dtype, device)``; ``ensure(length)``
-  arrangement   ``__init__(mixer, feed_forward, norm1, norm2)``; ``parts()``,
+  position      ``__init__(spec, dtype, device)``; ``ensure(length)`` -> True if device tables moved;
+                ``rotation()`` -> ``Rotation`` (tables, how many dimensions of a head they turn and
+                in which layout) for mixers that rotate queries and keys
+  arrangement   class attribute ``FAMILIES`` (part name -> family); ``__init__(parts: dict)``;
+                ``parts()``; attribute ``mixer`` (the part that owns the layer's cache entry);
                 ``__call__(residual, pending, ctx, entry, writes_cache)`` -> ``(residual, pending)``
 """
 

@@ -11,9 +11,24 @@ so that they are the same bits on every machine, and grow on demand.
 
 from __future__ import annotations
 
+from dataclasses import dataclass
+
 import torch
 
 from .base import Part
+
+
+@dataclass(frozen=True)
+class Rotation:
+    """What a mixer needs to rotate queries and keys: float32 tables ``[positions, rotary_dim / 2]``,
+    how many leading dimensions of a head they turn, and how the two halves of a pair lie in a head
+    (``"half_split"``: element ``j`` with element ``j + rotary_dim / 2``; ``"interleaved"``: ``2j``
+    with ``2j + 1``).  The kernels say which of these they take (``ops.rotation_tables``)."""
+
+    cos: torch.Tensor
+    sin: torch.Tensor
+    rotary_dim: int
+    layout: str = "half_split"
 
 
 class RotaryTable(Part):
@@ -32,6 +47,10 @@ class RotaryTable(Part):
         inv_freq = 1.0 / (theta ** exponent)
         pos = torch.arange(length, dtype=torch.int64).float()
         return torch.outer(pos, inv_freq)
+
+    def rotation(self) -> Rotation:
+        """The tables as they are now (call ``ensure`` first): the whole head, half-split."""
+        return Rotation(self.cos, self.sin, self.spec.head_dim, "half_split")
 
     def ensure(self, length: int) -> bool:
         """Make the tables cover positions ``[0, length)``; True if they moved (captured graphs that

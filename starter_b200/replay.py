@@ -36,13 +36,15 @@ def main(argv=None) -> int:
 
     print("[trace_run] starting (the first call compiles the kernels this model needs)",
           file=sys.stderr, flush=True)
+    from .cache.layout import PAGE_TOKENS, pages_for
     from .engine import ModelRunner, StepEntry, load_model
 
     os.makedirs(args.out, exist_ok=True)
     model = load_model(args.model, args.dtype)
-    pages = max((args.max_tokens + 63) // 64, 1)
-    runner = ModelRunner(model, pages * 64, max_sequences=min(pages, 4096), use_graphs=False)
-    print(f"[trace_run] model loaded; cache of {pages} pages of 64 tokens", file=sys.stderr, flush=True)
+    pages = max(pages_for(args.max_tokens), 1)
+    runner = ModelRunner(model, pages * PAGE_TOKENS, max_sequences=min(pages, 4096), use_graphs=False)
+    print(f"[trace_run] model loaded; cache of {pages} pages of {PAGE_TOKENS} tokens", file=sys.stderr,
+          flush=True)
 
     slots = {}
     for line in sys.stdin:

@@ -11,8 +11,11 @@ shapes.  The reference leaves all of this to ``from_pretrained``
 
 from __future__ import annotations
 
+from collections.abc import Mapping
+
 import torch
 
+from ..parts.base import role_of
 from .safetensors_io import open_model_files
 
 
@@ -41,7 +44,7 @@ def place(tensor: torch.Tensor, role: str, dtype, device) -> torch.Tensor:
     """Move one stored tensor to the device in the dtype its role calls for."""
     if not tensor.dtype.is_floating_point:
         return tensor.to(device=device, dtype=torch.int32)
-    if role == "gain" and tensor.dtype in (torch.float32, torch.float64):
+    if role_of(role).keep_32bit and tensor.dtype in (torch.float32, torch.float64):
         return tensor.to(device=device, dtype=torch.float32)
     return tensor.to(device=device, dtype=dtype)
 
@@ -57,8 +60,33 @@ def check_names(expected: dict, stored: dict, optional=()):
     return missing, unexpected, wrong, other
 
 
-def load_checkpoint(model_dir: str, expected: dict, dtype, device, tied_alias=None) -> dict:
-    """Return ``{name: device tensor}`` for every expected name.
+class CheckpointTensors(Mapping):
+    """``tensors[name]`` reads one stored tensor and places it on the device, when it is asked for and
+    not before: a model that stacks q/k/v and gate/up layer by layer then never holds much more than
+    one copy of the weights (the reference fuses layer by layer for the same reason,
+    engine/engine.py:157-165)."""
+
+    def __init__(self, owners: dict, expected: dict, dtype, device):
+        self._owners, self._expected, self._dtype, self._device = owners, expected, dtype, device
+
+    def __iter__(self):
+        return iter(self._expected)
+
+    def __len__(self) -> int:
+        return len(self._expected)
+
+    def __getitem__(self, name):
+        spec = self._expected[name]
+        return place(self._owners[name].tensor(name), spec.role, self._dtype, self._device)
+
+    def pop(self, name, default=None):
+        """Nothing is kept, so there is nothing to let go of."""
+        return default
+
+
+def load_checkpoint(model_dir: str, expected: dict, dtype, device, tied_alias=None):
+    """Check the checkpoint against ``expected`` and return a mapping ``name -> device tensor`` that
+    reads and places each tensor when it is indexed.
 
     ``tied_alias = (alias, target)``: ``alias`` is not expected; if the checkpoint
     holds it anyway it must equal ``target`` exactly, else that is reported.
@@ -74,7 +102,4 @@ def load_checkpoint(model_dir: str, expected: dict, dtype, device, tied_alias=No
             other.append(f"{alias} is stored and differs from {target}, but the config ties them")
     if missing or unexpected or wrong or other:
         raise WeightError(missing, unexpected, wrong, other)
-    out = {}
-    for name, spec in expected.items():
-        out[name] = place(owners[name].tensor(name), spec.role, dtype, device)
-    return out
+    return CheckpointTensors(owners, expected, dtype, device)

@@ -1,6 +1,7 @@
 """Random weights from a configuration and a seed, as tensors or as a model folder on disk.
 
-Matrices are N(0, 0.02); norm gains are 1 + N(0, 0.1).  Each tensor is drawn in
+Matrices are N(0, 0.02); norm gains are 1 + N(0, 0.1); every other kind of tensor is drawn as its
+role says (``starter_b200.parts.base.ROLES``), and a role nobody registered is an error.  Each tensor is drawn in
 float32 from a generator of its own, seeded from the seed and the tensor's name,
 so a tensor's values depend on nothing but (seed, name, shape) and the order of
 generation does not matter.  (The reference's test draws N(0, 0.05) for every
@@ -12,13 +13,12 @@ from __future__ import annotations
 import json
 import os
 import zlib
+from collections.abc import Mapping
 
 import torch
 
+from ..parts.base import role_of
 from .safetensors_io import write_safetensors
-
-MATRIX_STD = 0.02
-GAIN_STD = 0.1
 
 
 def _generator(seed: int, name: str, device) -> torch.Generator:
@@ -30,16 +30,36 @@ def _generator(seed: int, name: str, device) -> torch.Generator:
 def random_tensor(seed: int, name: str, spec, dtype, device="cpu") -> torch.Tensor:
     gen = _generator(seed, name, device)
     values = torch.randn(tuple(spec.shape), generator=gen, dtype=torch.float32, device=device)
-    if spec.role == "gain":
-        values.mul_(GAIN_STD).add_(1.0)
-    else:
-        values.mul_(MATRIX_STD)
+    role = role_of(spec.role)
+    values.mul_(role.std).add_(role.mean)
     return values.to(dtype)
 
 
-def random_checkpoint(expected: dict, seed: int, dtype, device="cpu") -> dict:
-    """``{name: tensor}`` for every expected name (values differ between CPU and CUDA generators)."""
-    return {name: random_tensor(seed, name, spec, dtype, device) for name, spec in expected.items()}
+class RandomTensors(Mapping):
+    """``tensors[name]`` draws that tensor when it is asked for (the same values every time: they
+    depend on nothing but the seed, the name and the shape), so a model that takes its tensors layer
+    by layer never holds more than it keeps."""
+
+    def __init__(self, expected: dict, seed: int, dtype, device):
+        self._expected, self._seed, self._dtype, self._device = expected, seed, dtype, device
+
+    def __iter__(self):
+        return iter(self._expected)
+
+    def __len__(self) -> int:
+        return len(self._expected)
+
+    def __getitem__(self, name):
+        return random_tensor(self._seed, name, self._expected[name], self._dtype, self._device)
+
+    def pop(self, name, default=None):
+        return default
+
+
+def random_checkpoint(expected: dict, seed: int, dtype, device="cpu") -> RandomTensors:
+    """A mapping ``name -> tensor`` over every expected name (values differ between CPU and CUDA
+    generators)."""
+    return RandomTensors(expected, seed, dtype, device)
 
 
 def write_model_folder(path: str, config, seed: int, dtype=torch.float32) -> str:

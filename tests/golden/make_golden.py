@@ -1,5 +1,5 @@
 """Runs the reference's OWN forward code (engine/engine.py of alvinyuwen/starter) on the CPU in
-float32 on tiny random models and stores its logits, so that tests can hold the plain
+float32 and in bfloat16 on tiny random models and stores its logits, so that tests can hold the plain
 implementation (tests/plain_qwen3.py) against them without the reference being present.
 
     python tests/golden/make_golden.py /path/to/reference
@@ -10,9 +10,10 @@ no longer has ``config.rope_theta`` (engine/engine.py:146), so the engine object
 from a model folder written by ``starter_b200.weights.write_model_folder``.  Only the reference's
 own functions compute: ``_grow_rope``, ``_ensure_shape``, ``_forward_prefill`` (hence ``_block``,
 ``rms_norm``, ``apply_rope``, ``_sdpa``).  It returns logits of the last position only, so every
-position is obtained by running every prefix.  Output: ``reference_logits.json`` (a few KB) with,
-per case, the config, the seed, the prompt and the float32 logits ``[T, vocab]`` rounded to 9
-significant digits.
+position is obtained by running every prefix.  Output: ``reference_logits.json`` with, per case,
+the config, the seed, the prompt, the float32 logits ``[T, vocab]`` rounded to 9 significant digits
+and ``logits_bf16``: the same run with the reference's ``LOAD_DTYPE`` left at bfloat16
+(engine/engine.py:41-43), which pins where the reference rounds to its working type.
 """
 
 import json
@@ -32,12 +33,14 @@ import plain_qwen3 as plain  # noqa: E402
 CASES = [("A", 11, 9), ("B", 12, 7), ("C", 13, 6)]  # (config, weight seed, prompt length)
 
 
-def reference_engine(ref_root, cfg, w):
-    sys.path.insert(0, os.path.join(ref_root, "engine"))
+def reference_engine(ref_root, cfg, w, dtype=torch.float32):
+    if os.path.join(ref_root, "engine") not in sys.path:
+        sys.path.insert(0, os.path.join(ref_root, "engine"))
     import engine as ref  # the reference's engine/engine.py
 
     ref.DEVICE = "cpu"
-    ref.LOAD_DTYPE = torch.float32
+    ref.LOAD_DTYPE = dtype
+    w = {k: v.to(dtype) for k, v in w.items()}
     e = ref.Engine.__new__(ref.Engine)
     e.LAYERS = cfg["num_hidden_layers"]
     e.HIDDEN = cfg["hidden_size"]
@@ -67,7 +70,7 @@ def reference_engine(ref_root, cfg, w):
             "down": w[p + "mlp.down_proj.weight"],
         })
     e.transposed = {}
-    e.dtype = torch.float32
+    e.dtype = dtype
     e.cuda = False
     e.q_size = e.HEADS * e.HEAD_DIM
     e.kv_size = e.KV_HEADS * e.HEAD_DIM
@@ -91,8 +94,21 @@ def reference_engine(ref_root, cfg, w):
     return e
 
 
+def reference_rows(ref_root, cfg, w, prompt, dtype):
+    e = reference_engine(ref_root, cfg, w, dtype)
+    rows = []
+    with torch.inference_mode():
+        for t in range(1, len(prompt) + 1):
+            ids = torch.tensor([prompt[:t]], dtype=torch.int64)
+            e._ensure_shape(1, t, 1)
+            rows.append(e._forward_prefill(ids, t)[0, -1].float())
+    return torch.stack(rows)
+
+
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py /path/to/the/reference/checkout")
+    ref_root = sys.argv[1]
     out = {"note": "logits of alvinyuwen/starter engine/engine.py run on CPU in float32", "cases": []}
     tmp = tempfile.mkdtemp()
     for name, seed, length in CASES:
@@ -100,20 +116,20 @@ def main():
         folder = make_folder(tmp, name, seed=seed, use_sliding_window=False, sliding_window=None)
         cfg, w = plain.read_model_folder(folder)
         prompt = random_prompt(length, cfg["vocab_size"], seed + 100)
-        e = reference_engine(ref_root, cfg, w)
-        rows = []
-        with torch.inference_mode():
-            for t in range(1, length + 1):
-                ids = torch.tensor([prompt[:t]], dtype=torch.int64)
-                e._ensure_shape(1, t, 1)
-                rows.append(e._forward_prefill(ids, t)[0, -1].float())
-        ref_logits = torch.stack(rows)
+        ref_logits = reference_rows(ref_root, cfg, w, prompt, torch.float32)
         mine = plain.plain_forward(cfg, w, prompt)
         print(name, "plain vs reference code: max abs diff", (mine - ref_logits).abs().max().item())
+        ref_bf16 = reference_rows(ref_root, cfg, w, prompt, torch.bfloat16)
+        w16 = {k: v.to(torch.bfloat16) for k, v in w.items()}
+        mine16 = plain.plain_forward(cfg, w16, prompt)
+        print(name, "the same in bfloat16: max abs diff", (mine16 - ref_bf16).abs().max().item(),
+              "of max |logit|", ref_bf16.abs().max().item(),
+              "; bfloat16 vs float32 reference:", (ref_bf16 - ref_logits).abs().max().item())
         out["cases"].append({
             "config": name, "seed": seed, "prompt": prompt,
             "overrides": {"use_sliding_window": False, "sliding_window": None},
             "logits": [[float(f"{v:.9g}") for v in row] for row in ref_logits.tolist()],
+            "logits_bf16": [[float(f"{v:.5g}") for v in row] for row in ref_bf16.tolist()],
         })
     with open(os.path.join(HERE, "reference_logits.json"), "w") as handle:
         json.dump(out, handle, separators=(",", ":"))

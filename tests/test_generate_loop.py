@@ -176,3 +176,100 @@ def test_slots_are_closed_when_a_step_fails():
     with pytest.raises(RuntimeError):
         loop.run_batch([Request([1, 2], 5), Request([3], 5)])
     assert runner.seqs == {}
+
+
+# ----------------------------------------------------------------------------- one step of lookahead
+
+class LookaheadRunner(ScriptedRunner):
+    """A scripted runner that, like the device, keeps the token it drew as each sequence's next input
+    and hands tokens out through handles; it writes down when steps are launched and when read."""
+
+    def __init__(self, slots=8):
+        super().__init__(slots)
+        self.log = []
+        self.drawn = {}          # slot -> the token drawn last for it (what the device would hold)
+        self.count = 0
+
+    def start_step(self, entries, sampler, temperatures, keys, positions):
+        from starter_b200.engine.batch import FED, StepEntry
+
+        single = all(len(e.tokens) == 1 for e in entries)
+        number = self.count
+        self.count += 1
+        filled = []
+        for e in entries:
+            if e.tokens[0] is FED:
+                assert single and e.slot in self.drawn, "no device-held token for this sequence"
+                filled.append(StepEntry(e.slot, [self.drawn[e.slot]], e.want))
+            else:
+                filled.append(e)
+        self.log.append(("launch", number, [e.tokens[0] is FED for e in entries]))
+        tokens = sampler.select(self.step(filled), temperatures, keys, positions)
+        for e, t in zip(entries, tokens):
+            self.drawn[e.slot] = t
+        runner = self
+
+        class Handle:
+            device_feeds = single
+
+            def result(self):
+                runner.log.append(("read", number))
+                return tokens
+
+        return Handle()
+
+
+def test_the_next_step_is_launched_before_this_steps_tokens_are_read():
+    runner = LookaheadRunner()
+    loop = GenerationLoop(runner, HostSampler(), max_batch=4, max_pages=100)
+    prompts = [[3, 1, 4], [1, 5]]
+    done = loop.run_batch([Request(p, 5) for p in prompts])
+    assert [d.tokens for d in done] == [expected(p, 5) for p in prompts]
+    # step 0 (the prompts) is read before step 1 goes out with host tokens; from then on every step
+    # is launched, with device-held tokens, before the step before it is read; the last token needs
+    # no step of its own (5 tokens: the prompt step and four more)
+    assert runner.log == [
+        ("launch", 0, [False, False]), ("read", 0),
+        ("launch", 1, [False, False]),
+        ("launch", 2, [True, True]), ("read", 1),
+        ("launch", 3, [True, True]), ("read", 2),
+        ("launch", 4, [True, True]), ("read", 3),
+        ("read", 4),
+    ]
+    assert sorted(runner.closed) == [0, 1] and not runner.seqs
+
+
+def test_no_lookahead_where_a_token_can_end_a_sequence_or_the_batch_changes():
+    runner = LookaheadRunner()
+    loop = GenerationLoop(runner, HostSampler(), max_batch=4, max_pages=100)
+    prompts = [[3, 1, 4], [1, 5]]
+    # a stop token may end a sequence at any step: every step is read before the next goes out
+    want = expected(prompts[0], 6)
+    done = loop.run_batch([Request(prompts[0], 6, stop_token_ids={want[3]}), Request(prompts[1], 6)])
+    assert done[0].tokens == want[:4] and done[0].finish_reason == "stop"
+    assert done[1].tokens == expected(prompts[1], 6)
+    launches = [e for e in runner.log if e[0] == "launch"]
+    reads = [e for e in runner.log if e[0] == "read"]
+    assert all(runner.log.index(("read", n)) < runner.log.index(launches[n + 1]) for n in range(4))
+    # ... until the request that could stop has left; the other then runs ahead
+    assert any(flags == [True] for _, _, flags in launches)
+    # unequal lengths without stop tokens: the step in which one sequence ends is read before the
+    # next (smaller) batch is launched with host tokens, and nothing runs for a finished sequence
+    runner = LookaheadRunner()
+    loop = GenerationLoop(runner, HostSampler(), max_batch=4, max_pages=100)
+    done = loop.run_batch([Request(prompts[0], 2), Request(prompts[1], 5)])
+    assert [d.tokens for d in done] == [expected(prompts[0], 2), expected(prompts[1], 5)]
+    assert runner.log == [
+        ("launch", 0, [False, False]), ("read", 0),
+        ("launch", 1, [False, False]), ("read", 1),       # request 0 ends here: no lookahead
+        ("launch", 2, [False]),
+        ("launch", 3, [True]), ("read", 2),
+        ("launch", 4, [True]), ("read", 3),
+        ("read", 4),
+    ]
+    # with the option off, every step is read before the next is launched, and the tokens are the same
+    runner = LookaheadRunner()
+    loop = GenerationLoop(runner, HostSampler(), max_batch=4, max_pages=100, lookahead=False)
+    done = loop.run_batch([Request(p, 5) for p in prompts])
+    assert [d.tokens for d in done] == [expected(p, 5) for p in prompts]
+    assert [e[0] for e in runner.log] == ["launch", "read"] * 5

@@ -339,6 +339,36 @@ def test_tensor_core_product(rows, n, k, gated, bm, splits):
     assert status.item() == 0
 
 
+@pytest.mark.parametrize("rows,n,k,gated,splits,stage", [(8, 256, 512, False, 1, 0), (8, 384, 1024, False, 4, 1),
+                                                       (16, 128, 768, True, 2, 2)])
+def test_a_wait_in_the_tensor_core_product_that_runs_out_is_reported(rows, n, k, gated, splits, stage):
+    """One activation copy of every block is left out on purpose (an entry point made for this), so
+    the stage it belongs to never completes: the wait on it gives up after 2 ms, the kernel returns,
+    the status word says so and ``check_status`` turns it into an error.  The device stays usable:
+    the same product, run normally afterwards, is right."""
+    from starter_b200 import ops
+    from starter_b200.engine.runner import ModelRunner
+
+    x = rand(rows, k, dtype="bfloat16", seed=60)
+    w = rand(n * (2 if gated else 1), k, dtype="bfloat16", seed=61, scale=0.05)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.linear_tensor_core(dev(x), dev(w), gated=gated, bm=16, splits=splits, stages=4, status=status,
+                           withhold=(stage, 2_000_000))
+    torch.cuda.synchronize()
+    assert status.item() == 4
+    holder = ModelRunner.__new__(ModelRunner)         # check_status needs nothing but the word
+    holder.status = status
+    with pytest.raises(RuntimeError, match="tensor-core product ran out of time"):
+        holder.check_status()
+    assert status.item() == 0
+    got = ops.linear_tensor_core(dev(x), dev(w), gated=gated, bm=16, splits=splits, stages=4, status=status)
+    ref = x.double() @ w.double().t()
+    if gated:
+        gu = ref.to(torch.bfloat16)
+        ref = plain.plain_swiglu(gu[:, :n], gu[:, n:]).double()
+    assert torch.allclose(got.cpu().double(), ref, atol=2e-2, rtol=2e-2) and status.item() == 0
+
+
 @pytest.mark.parametrize("heads,kv_heads,d,window", [(4, 2, 16, None), (6, 2, 32, 5), (8, 8, 128, None),
                                                     (8, 1, 64, 70), (32, 8, 128, None), (4, 4, 64, 64),
                                                     (6, 3, 128, 130)])

@@ -232,3 +232,26 @@ def test_temperature_stop_tokens_and_batches_through_the_entry_point(tmp_path_fa
     assert done[1].tokens == want[1][:3]
     assert engine.runner.cache.slots.held_count == 0
     engine.runner.cache.check()
+
+
+@pytest.mark.parametrize("name", CONFIGS)
+def test_bfloat16_engine_against_the_plain_implementation_run_in_bfloat16(tmp_path_factory, name):
+    """The plain implementation with bfloat16 weights and activations rounds where the reference
+    rounds (it is held to the reference's own bfloat16 run in tests/test_plain.py); the bfloat16
+    engine is held to it, whole and one token at a time, as to the float32 oracle."""
+    from starter_b200.engine import StepEntry
+
+    _, cfg, w = model_case(tmp_path_factory, name)
+    w16 = {k: v.to(torch.bfloat16) for k, v in w.items()}
+    runner = runner_for(tmp_path_factory, name, "bfloat16")
+    seq = random_prompt(150, cfg["vocab_size"], 61)
+    want = plain.plain_forward(cfg, w16, seq)
+    slot = runner.open_sequence()
+    got = runner.step([StepEntry(slot, seq, all_places(len(seq)))])
+    runner.close_sequence(slot)
+    assert_close(got, want, "bfloat16", f"{name} whole, against the plain bfloat16 run")
+    slot = runner.open_sequence()
+    rows = [runner.step([StepEntry(slot, seq[:100], all_places(100))])]
+    rows += [runner.step([StepEntry(slot, [t], [0])]) for t in seq[100:]]
+    runner.close_sequence(slot)
+    assert_close(torch.cat(rows), want, "bfloat16", f"{name} 100 + 50 x 1, against the plain bfloat16 run")

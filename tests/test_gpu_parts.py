@@ -108,6 +108,15 @@ class RunningMeanMixer:
     def __call__(self, x, ctx, entry, writes_cache=True):
         state = ctx.cache.entry_state(entry)
         h = self.spec.hidden_size
+        if ctx.host is None:
+            # a captured step: one token per sequence, nothing of the host may steer it; row i
+            # belongs to the sequence in ctx.seq_slot[i]
+            slots = ctx.seq_slot.long()
+            sums = state[slots, :h] + x.float()
+            counts = state[slots, h] + 1
+            state[slots, :h] = sums
+            state[slots, h] = counts
+            return (sums / counts[:, None]).to(x.dtype) @ self.w.t()
         means = torch.empty_like(x, dtype=torch.float32)
         for slot, start, n in zip(ctx.host["seq_slot"].tolist(), ctx.host["seq_q_start"].tolist(),
                                   ctx.host["seq_q_len"].tolist()):
@@ -120,16 +129,16 @@ class RunningMeanMixer:
         return (means.to(x.dtype) @ self.w.t())
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
-def test_a_toy_mixer_with_state_registers_builds_and_steps(dtype):
-    from starter_b200.config import (GatedFeedForwardSpec, LayerSpec, ModelSpec, NormSpec, RopeSpec,
-                                     AttentionSpec, ScheduleEntry)
-    from starter_b200.engine import DecoderModel, ModelRunner, StepEntry
+def toy_state_model(dtype, hidden=48, vocab=101):
+    """Toy mixer, attention, the toy mixer again (its weights shared, a state of its own), and the
+    attention once more reading the keys its first run wrote."""
+    from starter_b200.config import (AttentionSpec, GatedFeedForwardSpec, ModelSpec, NormSpec, RopeSpec,
+                                     ScheduleEntry, prenorm_layer)
+    from starter_b200.engine import DecoderModel
     from starter_b200.parts import register
     from starter_b200.weights import random_checkpoint
 
     register("mixer", "toy_running_mean", RunningMeanMixer)
-    hidden, vocab = 48, 101
     norm = NormSpec(hidden, 1e-5)
     ff = GatedFeedForwardSpec(hidden, 80)
     attn = AttentionSpec(hidden, 3, 1, 16, 0.25, True, 1e-5, RopeSpec(16, 1e4))
@@ -141,16 +150,22 @@ def test_a_toy_mixer_with_state_registers_builds_and_steps(dtype):
         return out
 
     layers = (
-        LayerSpec(RunningMeanSpec(hidden), ff, norm, norm, names(0, ["w"])),
-        LayerSpec(attn, ff, norm, norm, names(1, ["q", "k", "v", "o", "q_norm", "k_norm"])),
+        prenorm_layer(RunningMeanSpec(hidden), ff, norm, norm, names(0, ["w"])),
+        prenorm_layer(attn, ff, norm, norm, names(1, ["q", "k", "v", "o", "q_norm", "k_norm"])),
     )
-    # run order: toy, attention, toy again (its weights shared, a state of its own), and attention
-    # once more reading the keys its first run wrote
     schedule = (ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(0, 2), ScheduleEntry(1, 1, writes_cache=False))
     spec = ModelSpec("Toy", vocab, hidden, layers, schedule, norm, True, "embed", "final", "head")
     model = DecoderModel(spec, DT[dtype], "cuda")
     tensors = random_checkpoint(model.expected_tensors(), 3, DT[dtype], "cuda")
     model.load_tensors(tensors)
+    return model, tensors, vocab
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_toy_mixer_with_state_registers_builds_and_steps(dtype):
+    from starter_b200.engine import ModelRunner, StepEntry
+
+    model, tensors, vocab = toy_state_model(dtype)
     assert model.kv_needs()[0] is None and model.kv_needs()[1] is not None
     runner = ModelRunner(model, max_tokens=64 * 8, max_sequences=4)
     assert set(runner.cache.state) == {0, 2} and len(runner.cache.groups) == 1
@@ -179,6 +194,141 @@ def test_a_toy_mixer_with_state_registers_builds_and_steps(dtype):
     ctx = runner.make_context([StepEntry(s, b, [])])
     got = model.blocks[0].mixer(model.blocks[0].norm1(model.embed[torch.tensor(b, device="cuda")].contiguous()), ctx, 0, True)
     assert_close(got, want, dtype, "toy mixer alone")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_the_toy_mixer_with_state_runs_in_the_captured_step(dtype):
+    """Generation (captured, self-feeding steps) with a mixer that keeps a running state: the graphs
+    are captured in the middle of generation, whenever the batch reaches a new length class, and the
+    warm-up runs of a capture must leave the state as they found it.  Tokens and the logits of every
+    step equal the eager run's."""
+    from starter_b200.engine.entry import Engine
+    from starter_b200.engine.generate import Request
+
+    model, _, vocab = toy_state_model(dtype)
+    prompts = [random_prompt(60, vocab, 11), random_prompt(20, vocab, 12), random_prompt(1, vocab, 13)]
+    new = 80      # every sequence crosses a page edge; the batch passes the classes of 1, 2 and 3 pages
+
+    def run(engine):
+        requests = [Request(list(p), new) for p in prompts]
+        loop = engine._ensure_room(requests, len(requests))
+        loop.lookahead = False        # each step's logits are read before the next step runs
+        tokens, rows = [], []
+        for n, step_out in enumerate(loop.stream_batch(requests)):
+            tokens.append([step_out[i] for i in range(len(prompts))])
+            graphs = engine.runner.graphs
+            if n > 0 and graphs is not None:
+                rows.append(graphs.logits[graphs.last_key].clone())
+        return tokens, rows
+
+    engine = Engine.from_model(model, max_batch=4)
+    captured, rows = run(engine)
+    assert len(engine.runner.graphs.graphs) >= 3
+    engine.runner.check_status()
+    # the eager run of the same loop, fed the captured run's tokens, step by step
+    from starter_b200.engine import StepEntry
+    runner = engine.runner
+    slots = [runner.open_sequence() for _ in prompts]
+    first = runner.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
+    assert first.argmax(-1).tolist() == captured[0]
+    for n, got in enumerate(rows):
+        eager = runner.step([StepEntry(s, [captured[n][i]], [0]) for i, s in enumerate(slots)])
+        assert_close(got, eager, dtype, f"captured against eager, step {n + 1}")
+        if dtype == "float32":
+            assert eager.argmax(-1).tolist() == captured[n + 1]
+    for s in slots:
+        runner.close_sequence(s)
+    again, _ = run(engine)                   # slots and states used again: nothing carried over
+    assert again == captured
+
+
+# ----------------------------------------------------------------------------- an arrangement of its own
+
+class SandwichBlock:
+    """A block with a third norm, on the mixer's output before it joins the residual stream:
+    ``x1 = x + norm3(mixer(norm1(x)))``, ``x2 = x1 + feed_forward(norm2(x1))``."""
+
+    FAMILIES = {"mixer": "mixer", "feed_forward": "feed_forward", "norm1": "norm", "norm2": "norm",
+                "norm3": "norm"}
+
+    def __init__(self, parts):
+        self._parts = dict(parts)
+        self.mixer = parts["mixer"]
+
+    def parts(self):
+        return dict(self._parts)
+
+    def __call__(self, residual, pending, ctx, entry, writes_cache=True):
+        p = self._parts
+        n = p["norm1"].add(residual, pending)
+        a = p["norm3"](p["mixer"](n, ctx, entry, writes_cache))
+        m = p["norm2"].add(residual, a)
+        return residual, p["feed_forward"](m, ctx)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_layer_with_three_norms_builds_from_its_spec(dtype):
+    from starter_b200.config import (AttentionSpec, GatedFeedForwardSpec, LayerSpec, ModelSpec, NormSpec,
+                                     RopeSpec, default_schedule)
+    from starter_b200.engine import DecoderModel, ModelRunner, StepEntry
+    from starter_b200.parts import register
+    from starter_b200.weights import random_checkpoint
+
+    register("arrangement", "toy_sandwich", SandwichBlock)
+    hidden, vocab = 64, 131
+    norm = NormSpec(hidden, 1e-6)
+    attn = AttentionSpec(hidden, 4, 2, 16, 0.25, True, 1e-6, RopeSpec(16, 1e4))
+    ff = GatedFeedForwardSpec(hidden, 96)
+    names = {f"mixer.{k}": f"a.{k}" for k in ("q", "k", "v", "o", "q_norm", "k_norm")}
+    names.update({f"feed_forward.{k}": f"f.{k}" for k in ("gate", "up", "down")})
+    names.update({f"norm{i}.weight": f"n{i}" for i in (1, 2, 3)})
+    layer = LayerSpec({"mixer": attn, "feed_forward": ff, "norm1": norm, "norm2": norm, "norm3": norm},
+                      names, arrangement="toy_sandwich")
+    spec = ModelSpec("Toy3", vocab, hidden, (layer,), default_schedule(1), norm, True, "embed", "final", "head")
+    model = DecoderModel(spec, DT[dtype], "cuda")
+    assert "n3" in model.expected_tensors()
+    tensors = random_checkpoint(model.expected_tensors(), 9, DT[dtype], "cuda")
+    model.load_tensors(tensors)
+    runner = ModelRunner(model, max_tokens=64 * 4, max_sequences=2)
+    seq = random_prompt(80, vocab, 4)
+    s = runner.open_sequence()
+    whole = runner.step([StepEntry(s, seq, list(range(80)))])
+    runner.close_sequence(s)
+    s = runner.open_sequence()
+    parts = [runner.step([StepEntry(s, seq[:50], list(range(50)))])]
+    parts += [runner.step([StepEntry(s, [t], [0])]) for t in seq[50:]]
+    assert_close(torch.cat(parts), whole, dtype, "sandwich layer, cut in steps")
+    # against plain torch: the plain block with the third norm put in
+    w = {k: v.cpu() for k, v in tensors.items()}
+    renamed = {f"L.self_attn.{k}_proj.weight": w[f"a.{k}"] for k in "qkvo"}
+    renamed.update({f"L.self_attn.{k}_norm.weight": w[f"a.{k}_norm"] for k in "qk"})
+    renamed.update({f"L.mlp.{k}_proj.weight": w[f"f.{k}"] for k in ("gate", "up", "down")})
+    cfg = dict(num_attention_heads=4, num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-6, hidden_size=hidden)
+    x = w["embed"][torch.tensor(seq)]
+    cos, sin = plain.plain_rope_tables(1e4, 16, len(seq), x.dtype)
+    a = plain.plain_mixer(plain.plain_rms_norm(x, w["n1"], 1e-6), renamed, "L.", cfg, cos, sin, None)
+    x = x + plain.plain_rms_norm(a, w["n3"], 1e-6)
+    x = x + plain.plain_feed_forward(plain.plain_rms_norm(x, w["n2"], 1e-6), renamed, "L.")
+    want = torch.nn.functional.linear(plain.plain_rms_norm(x, w["final"], 1e-6), w["embed"]).float()
+    assert_close(whole, want, dtype, "sandwich layer against plain torch")
+    # a layer spec that does not fit its arrangement is refused by name
+    bad = LayerSpec({"mixer": attn, "feed_forward": ff, "norm1": norm, "norm2": norm}, names, "toy_sandwich")
+    with pytest.raises(ValueError, match="norm3"):
+        DecoderModel(ModelSpec("T", vocab, hidden, (bad,), default_schedule(1), norm, True, "e", "f", "h"),
+                     DT[dtype], "cuda")
+
+
+def test_a_rotation_the_kernels_cannot_do_is_refused_by_name():
+    from starter_b200 import ops
+    from starter_b200.parts import Rotation
+
+    cos = torch.ones(8, 4, device="cuda")
+    assert ops.rotation_tables(None, 16) == (None, None)
+    assert ops.rotation_tables(Rotation(cos, cos, 8), 8)[0] is cos
+    with pytest.raises(ops.KernelError, match="half-split"):
+        ops.rotation_tables(Rotation(cos, cos, 8, "interleaved"), 8)
+    with pytest.raises(ops.KernelError, match="whole head"):
+        ops.rotation_tables(Rotation(cos, cos, 8), 16)
 
 
 # ----------------------------------------------------------------------------- more toy parts
@@ -258,8 +408,8 @@ def test_a_routed_feed_forward_and_another_position_encoding_plug_in(dtype):
     """A model whose layers differ: attention with scaled rotary positions + routed experts, then the
     library's attention with its own rotary positions + the dense feed-forward.  Built from specs,
     stepped whole and in pieces, and the first layer checked against plain torch."""
-    from starter_b200.config import (AttentionSpec, GatedFeedForwardSpec, LayerSpec, ModelSpec, NormSpec,
-                                     RopeSpec, default_schedule)
+    from starter_b200.config import (AttentionSpec, GatedFeedForwardSpec, ModelSpec, NormSpec,
+                                     RopeSpec, default_schedule, prenorm_layer)
     from starter_b200.engine import DecoderModel, ModelRunner, StepEntry
     from starter_b200.parts import register
     from starter_b200.weights import random_checkpoint
@@ -281,8 +431,8 @@ def test_a_routed_feed_forward_and_another_position_encoding_plug_in(dtype):
     routed = RoutedFeedForwardSpec(hidden, 48, 3)
     routed_names = ["router"] + [f"{k}{e}" for e in range(3) for k in ("gate_up", "down")]
     layers = (
-        LayerSpec(attn(ScaledRopeSpec(16, 1e4, 4.0)), routed, norm, norm, names(0, routed_names)),
-        LayerSpec(attn(RopeSpec(16, 1e4)), GatedFeedForwardSpec(hidden, 80), norm, norm, names(1, ["gate", "up", "down"])),
+        prenorm_layer(attn(ScaledRopeSpec(16, 1e4, 4.0)), routed, norm, norm, names(0, routed_names)),
+        prenorm_layer(attn(RopeSpec(16, 1e4)), GatedFeedForwardSpec(hidden, 80), norm, norm, names(1, ["gate", "up", "down"])),
     )
     spec = ModelSpec("Toy2", vocab, hidden, layers, default_schedule(2), norm, False, "embed", "final", "head")
     model = DecoderModel(spec, DT[dtype], "cuda")

@@ -67,25 +67,68 @@ def test_real_layer_sizes_whole_stepwise_and_batched(tmp_path_factory, dtype):
 
 
 def test_real_layer_sizes_graph_decode_of_a_full_batch(tmp_path_factory):
-    """Sixteen sequences decoded through the captured, self-feeding step: tokens equal to feeding the
-    same tokens step by step through the eager step function."""
+    """Sixteen sequences decoded through the captured, self-feeding step: the logits every replay
+    leaves, against the plain implementation and against the eager step fed the same tokens."""
     from starter_b200 import Engine
+    from starter_b200.engine import StepEntry
+    from starter_b200.engine.generate import Request
 
     folder, cfg, w = real_case(tmp_path_factory)
     prompts = [random_prompt(5 + 7 * i, cfg["vocab_size"], 700 + i) for i in range(16)]
     engine = Engine(folder, dtype="bfloat16", max_batch=16)
-    steps = list(engine.generate(prompts, 5))
-    engine.runner.graphs = None                       # the same loop without graphs
-    eager = list(engine.generate(prompts, 5))
-    margin = 3e-2 * 2
-    for i, prompt in enumerate(prompts[:4]):
-        seq = list(prompt)
-        for step in steps:
-            logits = plain.plain_forward(cfg, w, seq)[-1]
-            assert logits[step[i]].item() >= logits.max().item() - margin * max(1.0, logits.abs().max().item())
-            seq.append(step[i])
-    same = sum(a == b for s, e in zip(steps, eager) for a, b in zip(s, e))
-    assert same >= 0.9 * 16 * 5      # equal up to near-ties between bfloat16 logits
+    requests = [Request(list(p), 6) for p in prompts]
+    loop = engine._ensure_room(requests, len(requests))
+    loop.lookahead = False            # each step's logits are read before the next step runs
+    graphs = engine.runner.graphs
+    tokens, rows = [[] for _ in prompts], []
+    for n, step_out in enumerate(loop.stream_batch(requests)):
+        if n > 0:
+            rows.append(graphs.logits[graphs.last_key].clone())
+        for i in range(16):
+            tokens[i].append(step_out[i])
+    engine.runner.check_status()
+    assert len(rows) == 5
+    want = [plain.plain_forward(cfg, w, list(p) + t) for p, t in zip(prompts, tokens)]
+    for step, got in enumerate(rows):
+        ref = torch.stack([want[i][len(prompts[i]) + step] for i in range(16)])
+        assert_close(got, ref, "bfloat16", f"captured step {step} of 16 sequences")
+    # the eager step, fed the same tokens one by one, computes the same thing with the same kernels
+    runner = engine.runner
+    slots = [runner.open_sequence() for _ in prompts]
+    runner.step([StepEntry(s, p, []) for s, p in zip(slots, prompts)])
+    for step, got in enumerate(rows):
+        eager = runner.step([StepEntry(s, [t[step]], [0]) for s, t in zip(slots, tokens)])
+        assert_close(eager, got, "bfloat16", f"eager against captured, step {step}")
+    for s in slots:
+        runner.close_sequence(s)
+
+
+def test_real_layer_sizes_sixty_four_unequal_sequences(tmp_path_factory):
+    """A batch of 64 (the widest tiles of every product, one part per sequence in the attention):
+    the prompts in one step, then one eager and one captured single-token step, every row against
+    the plain implementation."""
+    from starter_b200.engine import ModelRunner, StepEntry, load_model
+
+    folder, cfg, w = real_case(tmp_path_factory)
+    vocab = cfg["vocab_size"]
+    seqs = [random_prompt(3 + 5 * i + 2, vocab, 1200 + i) for i in range(64)]     # prompt + 2 tokens
+    want = [plain.plain_forward(cfg, w, s) for s in seqs]
+    runner = ModelRunner(load_model(folder, "bfloat16"), max_tokens=64 * 6 * 64, max_sequences=64)
+    slots = [runner.open_sequence() for _ in seqs]
+    heads = [len(s) - 2 for s in seqs]
+    out = runner.step([StepEntry(s, q[:h], [h - 1]) for s, q, h in zip(slots, seqs, heads)])
+    assert_close(out, torch.stack([want[i][heads[i] - 1] for i in range(64)]), "bfloat16", "64 prompts, last places")
+    out = runner.step([StepEntry(s, [q[h]], [0]) for s, q, h in zip(slots, seqs, heads)])
+    assert_close(out, torch.stack([want[i][heads[i]] for i in range(64)]), "bfloat16", "64 rows, eager step")
+    runner.decode_tokens([StepEntry(s, [q[h + 1]], [0]) for s, q, h in zip(slots, seqs, heads)],
+                         [0.0] * 64, [0] * 64)
+    got = runner.graphs.logits[runner.graphs.last_key]
+    assert got.shape[0] == 64
+    assert_close(got, torch.stack([want[i][heads[i] + 1] for i in range(64)]), "bfloat16", "64 rows, captured step")
+    for s in slots:
+        runner.close_sequence(s)
+    runner.check_status()
+    runner.cache.check()
 
 
 def test_captured_decode_is_reproducible_over_many_steps(tmp_path_factory):

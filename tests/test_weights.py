@@ -118,3 +118,51 @@ def test_sharded_folder_and_duplicate_names(tmp_path):
     os.remove(os.path.join(folder, "model.safetensors.index.json"))
     with pytest.raises(ValueError, match="stored in both"):
         open_model_files(folder)
+
+
+def test_tensor_roles_are_open_and_an_unknown_role_is_an_error():
+    import pytest as _pytest
+    from starter_b200.parts import ParamSpec, Role, register_role
+    from starter_b200.weights.loader import place
+    from starter_b200.weights.random_init import random_tensor
+
+    with _pytest.raises(ValueError, match="no tensor role 'decay'"):
+        ParamSpec((4,), "decay")
+    # a bias is drawn around zero and, stored in 32-bit, stays 32-bit; a matrix follows the working type
+    bias = random_tensor(1, "b", ParamSpec((4000,), "bias"), torch.float32)
+    assert abs(bias.mean().item()) < 2e-3 and 0.018 < bias.std().item() < 0.022
+    assert place(bias, "bias", torch.bfloat16, "cpu").dtype == torch.float32
+    assert place(bias, "matrix", torch.bfloat16, "cpu").dtype == torch.bfloat16
+    state = random_tensor(1, "s", ParamSpec((4000,), "state"), torch.float32)
+    assert 0.09 < state.std().item() < 0.11
+    # a part with another kind of tensor registers its role
+    register_role("toy_decay", Role(mean=-1.0, std=0.5, keep_32bit=True))
+    decay = random_tensor(1, "d", ParamSpec((4000,), "toy_decay"), torch.float32)
+    assert -1.05 < decay.mean().item() < -0.95 and 0.45 < decay.std().item() < 0.55
+
+
+def test_a_layer_spec_must_fit_its_arrangement():
+    import pytest as _pytest
+    from starter_b200.config import GatedFeedForwardSpec, LayerSpec, ModelSpec, NormSpec, default_schedule
+    from starter_b200.config import AttentionSpec, RopeSpec
+    from starter_b200.engine.model import expected_tensors
+
+    norm = NormSpec(32, 1e-6)
+    attn = AttentionSpec(32, 2, 1, 16, 0.25, False, 1e-6, RopeSpec(16, 1e4))
+    ff = GatedFeedForwardSpec(32, 48)
+    names = {"mixer.q": "q", "mixer.k": "k", "mixer.v": "v", "mixer.o": "o", "feed_forward.gate": "g",
+             "feed_forward.up": "u", "feed_forward.down": "d", "norm1.weight": "n1", "norm2.weight": "n2"}
+
+    def spec_of(layer):
+        return ModelSpec("T", 50, 32, (layer,), default_schedule(1), norm, True, "e", "f", "h")
+
+    good = LayerSpec({"mixer": attn, "feed_forward": ff, "norm1": norm, "norm2": norm}, names)
+    assert good.mixer is attn and good.norm2 is norm
+    assert set(expected_tensors(spec_of(good))) == set(names.values()) | {"e", "f"}
+    with _pytest.raises(ValueError, match="lacks \\['norm2'\\]"):
+        expected_tensors(spec_of(LayerSpec({"mixer": attn, "feed_forward": ff, "norm1": norm}, names)))
+    with _pytest.raises(ValueError, match="has \\['norm9'\\] besides"):
+        expected_tensors(spec_of(LayerSpec({"mixer": attn, "feed_forward": ff, "norm1": norm, "norm2": norm,
+                                            "norm9": norm}, names)))
+    with _pytest.raises(AttributeError, match="no part named 'router'"):
+        good.router

@@ -69,6 +69,27 @@ def test_no_alloc_entry_point_matches_the_regular_one_twice_in_a_row():
         if call > 0:   # the first call loads the kernel's code; after that device memory must not move
             assert torch.cuda.mem_get_info()[0] == free_before
         assert torch.allclose(got.float(), want.float(), **TOL)
+    # calls that do go through the shared array (more than 8 parts are merged by a second kernel that
+    # reads them from it): two in a row, of different shapes, so that the second call's entries lie
+    # over the first call's at other offsets; several parts of the short sequences see no key at all
+    for seed, lengths, h, kvh, dim, splits in ((4, [500, 70, 1, 333], 8, 2, 64, 12),
+                                               (5, [129, 512, 64], 6, 3, 128, 20),
+                                               (6, [500, 70, 1, 333], 8, 2, 64, 12)):
+        c = _case(seed, lengths, h, kvh, dim)
+        want = ops.attention_decode(c["q"], c["ks"], c["vs"], c["table"], c["slot"], c["kv_len"], h, kvh,
+                                    dim, dim ** -0.5, None, splits)
+        # and, independent of any splitting, the plain row-by-row kernel
+        pos = (c["kv_len"] - 1).to(torch.int32)
+        plain = ops.attention_rowwise(c["q"], c["ks"], c["vs"], c["table"], c["slot"], pos, h, kvh, dim,
+                                      dim ** -0.5, None)
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
+        rc, got = _call(lib, c, h, kvh, dim, splits, out=torch.empty_like(c["q"]))
+        torch.cuda.synchronize()
+        assert rc == 0, lib.sb_attention_decode_noalloc_message()
+        assert torch.cuda.mem_get_info()[0] == free_before
+        assert torch.equal(got, want), "same kernels, same split: the scratch's place must not matter"
+        assert torch.allclose(got.float(), plain.float(), **TOL)
     # more scratch than the array holds is refused, with a message that says so, and nothing runs
     big = _case(3, [10] * 64, 32, 8, 128)
     rc, _ = _call(lib, big, 32, 8, 128, 32)
