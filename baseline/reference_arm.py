@@ -161,19 +161,20 @@ def run(args, sizes, context, prompt_len, decode_at, config_block, clock_sampler
         e2e = batch * steps / (t1 - t0)
         # the same steps on the device alone: its captured step replayed from the same position,
         # as its own _time_decode does (engine/engine.py:292-342)
-        e.g_pos.fill_(decode_at)
-        for _ in range(3):
-            e._decode_step()
-        e.g_pos.fill_(decode_at)
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        t0 = time.monotonic()
-        start.record()
-        for _ in range(steps):
-            e._decode_step()
-        stop.record()
-        torch.cuda.synchronize()
-        windows.append((t0, time.monotonic()))
+        with torch.inference_mode():
+            e.g_pos.fill_(decode_at)
+            for _ in range(3):
+                e._decode_step()
+            e.g_pos.fill_(decode_at)
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            t0 = time.monotonic()
+            start.record()
+            for _ in range(steps):
+                e._decode_step()
+            stop.record()
+            torch.cuda.synchronize()
+            windows.append((t0, time.monotonic()))
         return start.elapsed_time(stop) / steps, e2e
 
     try:
