@@ -585,3 +585,188 @@ def sample(logits, temperature=None, request_key=None, position=None, status=Non
         _ptr(feed[2] if feed else None), _ptr(cand_v), _ptr(cand_i), _stream())
     _check(rc, "sample", 2)
     return out
+
+
+# ---------------------------------------------------------------------------------------- chains
+
+CHAIN_MAX_ROWS = 64
+CHAIN_MAX_STAGES = 8
+CHAIN_MAX_LINEAR = 6
+CHAIN_STATUS_BIT = 32
+_chain_state = {}      # device index -> {"sync": int64[2], "partial": float32 arena}
+
+
+def _chain_scratch(device, floats: int):
+    """The chains of one device share two 64-bit words (grid-barrier counter, give-up flag) and one
+    float arena for partial tiles.  A chain writes the arena only after the kernel before it on the
+    stream has completed, so consecutive chains can use the same memory."""
+    state = _chain_state.get(device.index)
+    if state is None:
+        state = _chain_state[device.index] = {
+            "sync": torch.zeros((2,), dtype=torch.int64, device=device), "partial": None}
+    if state["partial"] is None or state["partial"].numel() < floats:
+        state["partial"] = torch.empty((max(floats, 1 << 20),), dtype=torch.float32, device=device)
+    return state["sync"], state["partial"]
+
+
+def reset_chains(device=None) -> None:
+    """Clear the chains' shared words after a chain gave up (its barrier count is then off and every
+    later chain on the device gives up at once until this is called)."""
+    for index, state in _chain_state.items():
+        if device is None or torch.device(device).index in (None, index):
+            state["sync"].zero_()
+
+
+class ChainValue:
+    """A ``[rows, width]`` bfloat16 tensor that a chain which is still open will produce.  ``resolve``
+    launches the chain and gives the tensor."""
+
+    __slots__ = ("chain", "stage", "tensor", "shape")
+
+    def __init__(self, chain, stage, tensor, shape):
+        self.chain, self.stage, self.tensor, self.shape = chain, stage, tensor, shape
+
+    @property
+    def dtype(self):
+        return torch.bfloat16
+
+
+def resolve(value):
+    """The tensor behind ``value``: a tensor as it is, a ``ChainValue`` after its chain has run."""
+    if isinstance(value, ChainValue):
+        value.chain.close()
+        if value.tensor is None:
+            raise KernelError("this value was summed straight into the norm after it and was never stored")
+        return value.tensor
+    return value
+
+
+def chain_takes_linear(x, weight, gated: bool) -> bool:
+    """Whether a chain can run ``x @ weight.T``: bfloat16, at most 64 rows, 16-byte aligned operands,
+    k a multiple of 8, a gated width a multiple of 64."""
+    rows, k_dim = x.shape
+    n_total = weight.shape[0]
+    if weight.dtype != torch.bfloat16 or x.dtype != torch.bfloat16 or not 1 <= rows <= CHAIN_MAX_ROWS:
+        return False
+    if k_dim % 8 or weight.data_ptr() % 16 or not weight.is_contiguous() or weight.shape[1] != k_dim:
+        return False
+    if gated and (n_total % 2 or (n_total // 2) % 64):
+        return False
+    return True
+
+
+def chain_takes_norm(hidden: int, gain) -> bool:
+    return hidden % 8 == 0 and hidden <= 16384 and gain.dtype in (torch.float32, torch.bfloat16) \
+        and gain.data_ptr() % 16 == 0
+
+
+class OpenChain:
+    """Few-row projections and row norms that run as ONE persistent kernel (csrc/dense_chain.cu).
+
+    Stages are added with ``linear`` and ``add_norm`` and run when the chain is closed (by ``close`` or
+    by ``resolve`` of one of its values).  A stage may read tensors that exist when the chain is
+    launched and values of earlier stages of the same chain."""
+
+    def __init__(self, rows: int, device, status=None):
+        if not 1 <= rows <= CHAIN_MAX_ROWS:
+            raise KernelError(f"a chain runs 1 to {CHAIN_MAX_ROWS} rows, not {rows}")
+        self.rows, self.device, self.status = rows, device, status
+        self.stages = []
+        self.closed = False
+        #: None, or a zeroed int64 tensor [ctas, 64]: each CTA's time stamps (ns) at its stage boundaries
+        self.trace = None
+        self.n_ctas = _lib("dense_chain").sb_dense_chain_ctas()
+        self.bm = 16 if rows <= 16 else 32 if rows <= 32 else 64
+
+    # ------------------------------------------------------------------ building
+
+    def room_for(self, linear: bool) -> bool:
+        if self.closed or len(self.stages) >= CHAIN_MAX_STAGES:
+            return False
+        return not linear or sum(s["kind"] == 0 for s in self.stages) < CHAIN_MAX_LINEAR
+
+    def _input(self, x, what):
+        """(tensor, keep-alive) of a stage input: a tensor, or a stored value of this chain."""
+        if isinstance(x, ChainValue):
+            if x.chain is not self:
+                return resolve(x)
+            if x.tensor is None:
+                raise KernelError(f"{what} was summed straight into a norm and cannot be read again")
+            return x.tensor
+        return x
+
+    def linear(self, x, weight, gated=False) -> ChainValue:
+        shape = x.shape
+        xt = self._input(x, "the input of a projection")
+        _need(xt, "x", torch.bfloat16, 2)
+        _need(weight, "weight", torch.bfloat16, 2)
+        if not chain_takes_linear(xt, weight, gated) or shape[0] != self.rows or not self.room_for(True):
+            raise KernelError("this projection does not fit the chain (see chain_takes_linear)")
+        n_out = weight.shape[0] // 2 if gated else weight.shape[0]
+        out = torch.empty((self.rows, n_out), dtype=torch.bfloat16, device=self.device)
+        parts = _lib("dense_chain").sb_dense_chain_parts(n_out, x.shape[1], int(gated), self.n_ctas)
+        tiles = n_out // 64 if gated else -(-n_out // 128)
+        self.stages.append({"kind": 0, "n_out": n_out, "k_dim": x.shape[1], "gated": int(gated), "store": 1,
+                            "x": xt, "w": weight, "out": out, "parts": parts,
+                            "floats": tiles * parts * self.bm * 128})
+        return ChainValue(self, len(self.stages) - 1, out, (self.rows, n_out))
+
+    def add_norm(self, residual, delta, gain, eps) -> ChainValue:
+        """``residual += delta`` (in place, rounded) and its RMSNorm; ``delta`` None norms ``residual``
+        alone; ``residual`` None norms ``delta`` alone.  A ``delta`` that is the value of the stage just
+        before, a plain projection, is summed from that stage's partial tiles and never stored."""
+        hidden = (residual if residual is not None else delta).shape[1]
+        if not chain_takes_norm(hidden, gain) or not self.room_for(False):
+            raise KernelError("this norm does not fit the chain (see chain_takes_norm)")
+        fused = (isinstance(delta, ChainValue) and delta.chain is self and delta.stage == len(self.stages) - 1
+                 and self.stages[-1]["kind"] == 0 and not self.stages[-1]["gated"] and delta.tensor is not None)
+        if fused:
+            self.stages[-1]["store"] = 0
+            self.stages[-1]["out"] = None
+            delta.tensor = None
+            dt = None
+        else:
+            dt = self._input(delta, "the delta of a norm") if delta is not None else None
+        if residual is not None:
+            _need(residual, "residual", torch.bfloat16, 2)
+        if dt is not None:
+            _need(dt, "delta", torch.bfloat16, 2)
+        normed = torch.empty((self.rows, hidden), dtype=torch.bfloat16, device=self.device)
+        self.stages.append({"kind": 1, "hidden": hidden, "gain": gain, "eps": float(eps), "residual": residual,
+                            "delta": dt, "normed": normed})
+        return ChainValue(self, len(self.stages) - 1, normed, (self.rows, hidden))
+
+    # ------------------------------------------------------------------ running
+
+    def close(self) -> None:
+        if self.closed:
+            return
+        self.closed = True
+        if not self.stages:
+            return
+        floats = sum(s.get("floats", 0) for s in self.stages)
+        sync, arena = _chain_scratch(self.device, floats)
+        desc = (ctypes.c_longlong * (16 * len(self.stages)))()
+        eps = (ctypes.c_float * len(self.stages))()
+        at = 0
+        for i, s in enumerate(self.stages):
+            d = [0] * 16
+            if s["kind"] == 0:
+                partial = arena.data_ptr() + 4 * at
+                at += s["floats"]
+                d[:10] = [0, s["n_out"], s["k_dim"], s["gated"], s["store"], s["x"].data_ptr(), s["w"].data_ptr(),
+                          s["out"].data_ptr() if s["out"] is not None else 0, partial, s["parts"]]
+            else:
+                d[:8] = [1, s["hidden"], int(s["gain"].dtype == torch.float32), int(s["residual"] is not None),
+                         s["residual"].data_ptr() if s["residual"] is not None else 0,
+                         s["delta"].data_ptr() if s["delta"] is not None else 0, s["gain"].data_ptr(),
+                         s["normed"].data_ptr()]
+                eps[i] = s["eps"]
+            for j, v in enumerate(d):
+                desc[16 * i + j] = v
+        rc = _lib("dense_chain").sb_dense_chain(
+            desc, eps, len(self.stages), self.rows, _ptr(sync), _ptr(self.status), ctypes.c_ulonglong(0),
+            _ptr(self.trace), _stream())
+        if rc in (-3, -4):
+            raise KernelError(f"the TMA descriptors for a chain could not be made (code {rc})")
+        _check(rc, "dense_chain")
