@@ -31,6 +31,13 @@ QWEN3_4B = dict(
     num_key_value_heads=8, head_dim=128, intermediate_size=9728, vocab_size=151936, rope_theta=5e6,
     rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=4096,
 )
+QWEN3_8B = dict(QWEN3_4B, hidden_size=4096, intermediate_size=12288, rope_theta=1e6, tie_word_embeddings=False)
+QWEN3_14B = dict(QWEN3_8B, num_hidden_layers=40, hidden_size=5120, num_attention_heads=40, intermediate_size=17408)
+#: the further rows of the measurement table: model sizes, and the generation workload quoted for each
+WORKLOADS = {
+    "8b": dict(config=QWEN3_8B, name="Qwen3-8B", batch=8, prompt_range=(512, 2048), new_tokens=256),
+    "14b": dict(config=QWEN3_14B, name="Qwen3-14B", batch=32, prompt_range=(1024, 1024), new_tokens=512),
+}
 CONTEXT = 4096
 PROMPT = 2048
 DECODE_AT = 3072  # 2,048 prompt tokens + 1,024 decoded: the middle of the generation range
@@ -122,6 +129,151 @@ def reference_arm(args) -> int:
                    config_block(args.layers, args.batch, peaks()["source"]), ClockSampler(), METRIC)
 
 
+def per_stage(model, runner, slots, batch, peak_gbs, out=sys.stderr):
+    """Where a decode step's time goes: every kind of kernel of a layer alone, in a CUDA graph that
+    runs it once per layer on that layer's own weights and cache (so nothing stays in L2 from one
+    launch to the next), timed with CUDA events; against the time its bytes take at the copy peak."""
+    import torch
+
+    from starter_b200 import ops
+
+    spec = model.spec
+    dev = model.device
+    blocks = [model.blocks[e.layer] for e in spec.schedule]
+    entries = [e.cache for e in spec.schedule]
+    mixer = blocks[0].mixer.spec
+    h = spec.hidden_size
+    x = (torch.randn(batch, h, device=dev) * 0.5).to(torch.bfloat16)
+    res = x.clone()
+    attn_in = (torch.randn(batch, mixer.num_heads * mixer.head_dim, device=dev) * 0.5).to(torch.bfloat16)
+    act = (torch.randn(batch, blocks[0].feed_forward.down.shape[1], device=dev) * 0.5).to(torch.bfloat16)
+    qkv = (torch.randn(batch, blocks[0].mixer.qkv.shape[0], device=dev) * 0.5).to(torch.bfloat16)
+    cache = runner.cache
+    seq_slot = torch.tensor(slots, dtype=torch.int32, device=dev)
+    kv_len = torch.tensor([cache.lengths[s] for s in slots], dtype=torch.int32, device=dev)
+    kv_tokens = max(cache.lengths[s] for s in slots)
+    rot = blocks[0].mixer.position.rotation()
+
+    def attention(b, entry):
+        keys, values = cache.entry_pages(entry)
+        m = b.mixer
+        return ops.attention_decode_qkv(qkv, keys, values, cache.block_table, seq_slot, kv_len, mixer.num_heads,
+                                        mixer.num_kv_heads, mixer.head_dim, mixer.scale, mixer.window, m.q_norm,
+                                        m.k_norm, mixer.qk_norm_eps, rot.cos, rot.sin, write_cache=True,
+                                        kv_hint=kv_tokens)
+
+    nbytes = lambda t: t.numel() * t.element_size()
+    kv_bytes = cache.bytes_per_token() // len(set(entries)) * int(kv_len.sum())
+    stages = [
+        ("sum + norm (x2 per layer)", lambda b, e: ops.rmsnorm(res, b.norm1.weight, b.norm1.spec.eps, delta=x), lambda b: 0),
+        ("q/k/v projection", lambda b, e: ops.linear(x, b.mixer.qkv), lambda b: nbytes(b.mixer.qkv)),
+        ("attention (norm, rotation, cache write inside)", attention, lambda b: kv_bytes),
+        ("output projection", lambda b, e: ops.linear(attn_in, b.mixer.o), lambda b: nbytes(b.mixer.o)),
+        ("gate/up projection + SwiGLU", lambda b, e: ops.linear(x, b.feed_forward.gate_up, gated=True),
+         lambda b: nbytes(b.feed_forward.gate_up)),
+        ("down projection", lambda b, e: ops.linear(act, b.feed_forward.down), lambda b: nbytes(b.feed_forward.down)),
+    ]
+    rows, total = [], 0.0
+    for name, fn, bytes_of in stages:
+        for b, e in zip(blocks, entries):
+            fn(b, e)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for b, e in zip(blocks, entries):
+                fn(b, e)
+        graph.replay()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(5):
+            graph.replay()
+        stop.record()
+        torch.cuda.synchronize()
+        us = start.elapsed_time(stop) / 5 / len(blocks) * 1e3
+        ideal = bytes_of(blocks[0]) / (peak_gbs * 1e9) * 1e6
+        per_layer = us * (2 if name.startswith("sum") else 1)
+        total += per_layer
+        rows.append((name, us, ideal))
+    print(f"decode step at batch {batch}, {kv_tokens} cached tokens per sequence: microseconds per launch, "
+          f"inside a CUDA graph", file=out)
+    for name, us, ideal in rows:
+        frac = f"{ideal / us:.2f}" if ideal else "-"
+        print(f"  {name:48s} {us:7.1f} us   bytes at {peak_gbs:.0f} GB/s: {ideal:6.1f} us   fraction {frac}", file=out)
+    print(f"  a layer's seven launches one by one: {total:.1f} us", file=out)
+    return total
+
+
+def workload(args) -> int:
+    """One of the further rows (``--workload 8b|14b``): a batch of prompts generated to the end through
+    ``Engine.generate``, timed by the wall clock with the device idle on both sides.  Prints one JSON
+    line: the whole job's generated tokens a second, the time to the first token (all prompts in one
+    step), decode tokens a second after it, and the decode's share of its own memory roofline."""
+    import torch
+
+    from starter_b200.config import config_from_dict
+    from starter_b200.engine import random_model
+    from starter_b200.engine.entry import Engine
+
+    spec = WORKLOADS[args.workload]
+    raw = dict(spec["config"])
+    layers_of_model = raw["num_hidden_layers"]
+    raw["num_hidden_layers"] = min(args.layers, layers_of_model) if args.layers_given else layers_of_model
+    config = config_from_dict(raw)
+    model = random_model(config, seed=0, dtype="bfloat16")
+    pk = peaks()
+    gen = torch.Generator().manual_seed(0)
+    lo, hi = spec["prompt_range"]
+    lengths = [int(torch.randint(lo, hi + 1, (1,), generator=gen)) for _ in range(spec["batch"])]
+    prompts = [torch.randint(0, config.vocab_size, (n,), generator=gen).tolist() for n in lengths]
+    new = spec["new_tokens"]
+    engine = Engine.from_model(model, max_batch=spec["batch"])
+    sampler = ClockSampler()
+    sampler.start()
+    for _ in engine.generate(prompts, 4):        # builds the cache, compiles, captures the first graphs
+        pass
+    best = None
+    for _ in range(2):
+        torch.cuda.synchronize()
+        t0 = time.monotonic()
+        stream = engine.generate(prompts, new)
+        next(stream)
+        torch.cuda.synchronize()
+        t1 = time.monotonic()
+        for _ in stream:
+            pass
+        torch.cuda.synchronize()
+        t2 = time.monotonic()
+        if best is None or t2 - t0 < best[2] - best[0]:
+            best = (t0, t1, t2)
+    t0, t1, t2 = best
+    engine.runner.check_status()
+    batch = spec["batch"]
+    decode_ms = (t2 - t1) / (new - 1) * 1e3
+    mean_context = sum(lengths) / batch + new / 2
+    step_bytes = model.step_weight_bytes() + engine.runner.cache.bytes_per_token() * batch * mean_context
+    achieved = step_bytes / (decode_ms * 1e-3) / 1e9
+    line = {
+        "metric": f"generated tok/s of the whole job ({spec['name']} BF16): {batch} prompts of {lo}-{hi} tokens, {new} new tokens each",
+        "value": round(batch * new / (t2 - t0), 1), "unit": "tok/s", "n_gpus": 1, "higher_is_better": True,
+        "dtype": "bf16", "data": "synthetic: random weights N(0,0.02), uniform random token ids",
+        "config": {"model": spec["name"], "layers": raw["num_hidden_layers"], "layers_of_model": layers_of_model,
+                   "hidden": raw["hidden_size"], "heads": raw["num_attention_heads"],
+                   "kv_heads": raw["num_key_value_heads"], "head_dim": raw["head_dim"],
+                   "intermediate": raw["intermediate_size"], "vocab": raw["vocab_size"],
+                   "tied": raw["tie_word_embeddings"], "global_batch": batch, "prompt_tokens": sum(lengths),
+                   "new_tokens": new, "peaks": pk["source"]},
+        "ttft_ms": round((t1 - t0) * 1e3, 2),
+        "prefill_tok_s": round(sum(lengths) / (t1 - t0), 1),
+        "decode_tok_s": round(batch / decode_ms * 1e3, 1), "decode_ms_per_step": round(decode_ms, 4),
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "clocks": sampler.stop([(t0, t2)]),
+    }
+    print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -132,12 +284,19 @@ def main() -> int:
                         help="fewer layers than the model has (both numbers are reported)")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
+    parser.add_argument("--workload", choices=sorted(WORKLOADS), default=None,
+                        help="instead of the default run: one of the further rows (other model sizes)")
+    parser.add_argument("--per-stage", action="store_true",
+                        help="also print where a decode step's time goes, kernel by kernel (stderr)")
     args = parser.parse_args()
-    if args.impl == "reference":
-        return reference_arm(args)
+    args.layers_given = "--layers" in sys.argv
     if args.gpus != 1:
         print(f"bench.py measures one GPU: this library has no multi-GPU path (asked for {args.gpus})")
         return 2
+    if args.impl == "reference":
+        return reference_arm(args)
+    if args.workload:
+        return workload(args)
     warmup = max(args.warmup, 3)
     steps = max(args.steps, 1)
 
@@ -210,8 +369,16 @@ def main() -> int:
 
         for _ in range(warmup):
             one()
+        if args.per_stage:
+            per_layer_us = per_stage(model, runner, slots, batch, pk["hbm_gbs"])
+            one()
         before = ops.launch_count
         ms = timed(one, steps)
+        if args.per_stage:
+            print(f"  the whole step: {ms * 1e3:.1f} us = {len(model.spec.schedule)} layers x "
+                  f"{(ms * 1e3) / len(model.spec.schedule):.1f} us (head, sampling and embedding included); "
+                  f"launched one by one the layers' kernels add up to {per_layer_us:.1f} us a layer",
+                  file=sys.stderr)
         per_graph = runner.graphs.kernels_per_replay.get(batch, 0)
         launches = steps * per_graph + (ops.launch_count - before)
         for s in slots:
