@@ -199,7 +199,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ seq_slot, const int* __restrict__ seq_q_start,
                             const int* __restrict__ seq_q_len, const int* __restrict__ seq_kv_len,
                             const int* __restrict__ tile_seq, const int* __restrict__ tile_first,
-                            int heads, int kv_heads, float scale_log2, int window, int* status) {
+                            int heads, int kv_heads, float scale_log2, int window, int* status, int list_of_blocks) {
   constexpr int DC = D / 64;                        // 64-element (128-byte) chunks of the head
   constexpr int SUB = 128 * 128;                    // bytes of a [128 rows x 128 bytes] sub-tile
   constexpr int Q_BYTES = DC * SUB;                 // one tile of 128 queries
@@ -217,7 +217,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
   const int tile = blockIdx.y, head = blockIdx.x;   // heads run fastest: the work list's order holds
   const int q_first = tile_first[tile];
-  if (q_first & 255) return;                         // the work list is in tiles of 64: four make one block
+  // the work list is either this kernel's own (one entry per block of 256 queries) or the common
+  // one in tiles of 64 queries, of which every fourth starts a block
+  if (!list_of_blocks && (q_first & 255)) return;
   const int seq = tile_seq[tile];
   const int q_len = seq_q_len[seq], kv_len = seq_kv_len[seq];
   const int rows_valid = min(2 * TC_BQ, q_len - q_first);
@@ -555,7 +557,8 @@ template <int D>
 static int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out,
                   const int* block_table, int table_stride, const int* seq_slot, const int* seq_q_start,
                   const int* seq_q_len, const int* seq_kv_len, const int* tile_seq, const int* tile_first,
-                  int n_tiles, int heads, int kv_heads, float scale, int window, int* status, cudaStream_t s) {
+                  int n_tiles, int heads, int kv_heads, float scale, int window, int* status, int list_of_blocks,
+                  cudaStream_t s) {
   constexpr int DC = D / 64;
   const int smem = (2 * DC + 4 + TC_RING * DC) * 128 * 128 + 1024;
   static bool configured = false;
@@ -566,19 +569,21 @@ static int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMa
   }
   return launch_dependent(attention_prefill_tc_kernel<D>, dim3(heads, n_tiles), dim3(TC_THREADS), smem, s, mq, mk,
                           mv, (bf16*)out, block_table, table_stride, seq_slot, seq_q_start, seq_q_len, seq_kv_len,
-                          tile_seq, tile_first, heads, kv_heads, scale * 1.4426950408889634f, window, status);
+                          tile_seq, tile_first, heads, kv_heads, scale * 1.4426950408889634f, window, status,
+                          list_of_blocks);
 }
 
 extern "C" {
 
 // Same contract as sb_attention_prefill; n_tokens rows in q/out, n_pages pages in the stores.
+// list_of_blocks: tile_seq/tile_first list blocks of 256 queries (else tiles of 64, see the kernel).
 // head_dim must be 64 or 128 (returns -2 otherwise).
 int sb_attention_prefill_tc(const void* q, void* out, const void* k_store, const void* v_store,
                             const int* block_table, int table_stride, const int* seq_slot,
                             const int* seq_q_start, const int* seq_q_len, const int* seq_kv_len,
                             const int* tile_seq, const int* tile_first, int n_tiles, int n_tokens,
                             int n_pages, int heads, int kv_heads, int head_dim, float scale, int window,
-                            int* status, cudaStream_t s) {
+                            int* status, int list_of_blocks, cudaStream_t s) {
   if (n_tiles == 0) return 0;
   if (kv_heads <= 0 || heads % kv_heads) return -2;
   if (head_dim != 64 && head_dim != 128) return -2;
@@ -592,7 +597,7 @@ int sb_attention_prefill_tc(const void* q, void* out, const void* k_store, const
   rc = make_map(&mv, v_store, kv_rows, head_dim, SB_PAGE_TOKENS);
   if (rc) return rc;
 #define ARGS mq, mk, mv, out, block_table, table_stride, seq_slot, seq_q_start, seq_q_len, seq_kv_len, \
-             tile_seq, tile_first, n_tiles, heads, kv_heads, scale, window, status, s
+             tile_seq, tile_first, n_tiles, heads, kv_heads, scale, window, status, list_of_blocks, s
   if (head_dim == 64) return launch<64>(ARGS);
   return launch<128>(ARGS);
 #undef ARGS

@@ -17,6 +17,7 @@ import torch
 
 
 QUERY_TILE = 64
+QUERY_BLOCK = 256      # what one block of the tensor-core prompt attention takes
 
 #: in place of a token id in a ``StepEntry``: "the token the device drew for this sequence in the step
 #: before" (a captured single-token step can go on from it before the host has seen it)
@@ -47,6 +48,8 @@ class StepContext:
     want_rows: torch.Tensor
     tile_seq: torch.Tensor      # work list of the many-token attention: per tile of 64 queries its
     tile_first: torch.Tensor    # sequence (index into the seq_* arrays) and its first query there
+    block_seq: torch.Tensor     # the same list in blocks of 256 queries (None: derive it from the tiles)
+    block_first: torch.Tensor
     max_q_len: int
     max_kv_len: int
     cache: object
@@ -97,10 +100,14 @@ def plan_step(entries, starts, vocab_size=None):
     tiles = [(kv_len[i] - q_len[i] + first, i, first)
              for i in range(len(entries)) for first in range(0, q_len[i], QUERY_TILE)]
     tiles.sort(key=lambda t: -t[0])
+    blocks = [(kv_len[i] - q_len[i] + first, i, first)
+              for i in range(len(entries)) for first in range(0, q_len[i], QUERY_BLOCK)]
+    blocks.sort(key=lambda t: -t[0])
     arrays = {
         "tokens": tokens, "tok_pos": tok_pos, "tok_slot": tok_slot, "seq_slot": slots,
         "seq_q_start": q_start, "seq_q_len": q_len, "seq_kv_len": kv_len, "want_rows": want_rows,
         "tile_seq": [t[1] for t in tiles], "tile_first": [t[2] for t in tiles],
+        "block_seq": [t[1] for t in blocks], "block_first": [t[2] for t in blocks],
     }
     return {k: np.asarray(v, dtype=np.int32) for k, v in arrays.items()}
 

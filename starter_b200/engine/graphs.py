@@ -82,6 +82,7 @@ class DecodeGraphs:
             seq_q_start=self.rows[:batch], seq_q_len=self.ones[:batch],
             seq_kv_len=self._field("kv_len", batch), want_rows=self.rows[:batch],
             tile_seq=self.rows[:batch], tile_first=self.zeros[:batch],
+            block_seq=self.rows[:batch], block_first=self.zeros[:batch],
             max_q_len=1, max_kv_len=self.kv_hint, cache=self.runner.cache, status=self.runner.status,
             host=None)
 

@@ -145,6 +145,7 @@ class ModelRunner:
             seq_slot=dev["seq_slot"], seq_q_start=dev["seq_q_start"], seq_q_len=dev["seq_q_len"],
             seq_kv_len=dev["seq_kv_len"], want_rows=dev["want_rows"],
             tile_seq=dev["tile_seq"], tile_first=dev["tile_first"],
+            block_seq=dev["block_seq"], block_first=dev["block_first"],
             max_q_len=int(arrays["seq_q_len"].max()), max_kv_len=max_kv,
             cache=cache, status=self.status, host=arrays)
 

@@ -370,14 +370,17 @@ PREFILL_HEAD_DIMS = (16, 32, 64, 128)
 
 def attention_prefill(q, k_store, v_store, block_table, seq_slot, seq_q_start, seq_q_len, seq_kv_len,
                       tile_seq, tile_first, heads, kv_heads, head_dim, scale, window=None, status=None,
-                      kernel=None, max_q_len=None):
+                      kernel=None, max_q_len=None, blocks=None):
     """Causal attention for steps with many tokens per sequence (bfloat16, tensor cores).
 
     ``q`` ``[T, heads * head_dim]`` packed by sequence; the ``seq_*`` arrays describe each sequence
     of the step, ``tile_seq``/``tile_first`` list the tiles of 64 queries.  Head sizes 64 and 128 run
     on the tcgen05 kernel (256 queries a block, S and O in tensor memory) when some sequence brings
     more than 128 queries (``max_q_len``, taken as large when not given); everything else runs on
-    the mma.sync kernel, which has the smaller blocks.  ``kernel`` ("tcgen05" or "mma") forces one."""
+    the mma.sync kernel, which has the smaller blocks.  ``kernel`` ("tcgen05" or "mma") forces one.
+    ``blocks = (block_seq, block_first)`` is the same work list in blocks of 256 queries, which is what
+    the tcgen05 kernel launches; without it that kernel is launched once per tile of 64 and three of
+    four launches find nothing to do."""
     _need(q, "q", torch.bfloat16, 2)
     if q.shape[1] != heads * head_dim:
         raise KernelError(f"q has width {q.shape[1]}, expected {heads * head_dim}")
@@ -402,12 +405,17 @@ def attention_prefill(q, k_store, v_store, block_table, seq_slot, seq_q_start, s
             raise KernelError(f"the tcgen05 prefill kernel takes head_dim {PREFILL_TC_HEAD_DIMS}, not {head_dim}")
         if not q.is_contiguous():
             raise KernelError("q must be contiguous")
+        own_list = blocks is not None and blocks[0] is not None
+        if own_list:
+            for name, t in (("block_seq", blocks[0]), ("block_first", blocks[1])):
+                _need(t, name, torch.int32, 1)
+        list_seq, list_first = blocks if own_list else (tile_seq, tile_first)
         rc = _lib("attention_prefill_tc").sb_attention_prefill_tc(
             _ptr(q), _ptr(out), _ptr(k_store), _ptr(v_store), _ptr(block_table), block_table.shape[1],
-            _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), _ptr(seq_kv_len), _ptr(tile_seq),
-            _ptr(tile_first), tile_seq.shape[0], q.shape[0], k_store.shape[0], heads, kv_heads, head_dim,
+            _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), _ptr(seq_kv_len), _ptr(list_seq),
+            _ptr(list_first), list_seq.shape[0], q.shape[0], k_store.shape[0], heads, kv_heads, head_dim,
             ctypes.c_float(scale), int(window or 0), _ptr(status) if status is not None else None,
-            _stream())
+            int(own_list), _stream())
         _check(rc, "attention_prefill_tc")
         return out
     rc = _lib("attention_prefill").sb_attention_prefill(

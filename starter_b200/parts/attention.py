@@ -99,7 +99,8 @@ class GroupedQueryAttention(Part):
             a = ops.attention_prefill(q, keys, values, cache.block_table, ctx.seq_slot, ctx.seq_q_start,
                                       ctx.seq_q_len, ctx.seq_kv_len, ctx.tile_seq, ctx.tile_first,
                                       s.num_heads, s.num_kv_heads, s.head_dim, s.scale, s.window,
-                                      status=ctx.status, max_q_len=ctx.max_q_len)
+                                      status=ctx.status, max_q_len=ctx.max_q_len,
+                                      blocks=(ctx.block_seq, ctx.block_first))
         else:
             a = ops.attention_rowwise(q, keys, values, cache.block_table, ctx.tok_slot, ctx.tok_pos,
                                       s.num_heads, s.num_kv_heads, s.head_dim, s.scale, s.window)

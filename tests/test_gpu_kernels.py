@@ -393,3 +393,12 @@ def test_attention_prefill_many_tokens_per_sequence(heads, kv_heads, d, window, 
                                 status=status, kernel=kernel)
     assert status.item() == 0
     assert torch.allclose(got.cpu().float(), c["want"].float(), atol=2e-2, rtol=2e-2)
+    if kernel == "tcgen05":
+        # the kernel's own work list (one entry per block of 256 queries): the same blocks, none idle
+        blocks = [(i, f) for i in range(len(new)) for f in range(0, new[i], 256)]
+        again = ops.attention_prefill(dev(c["q"]), dev(c["ks"]), dev(c["vs"]), dev(c["table"]),
+                                      ints(list(range(len(new)))), ints(q_start), ints(new), ints(lengths),
+                                      ints([t[0] for t in tiles]), ints([t[1] for t in tiles]), heads, kv_heads, d,
+                                      c["scale"], window, status=status, kernel=kernel,
+                                      blocks=(ints([b[0] for b in blocks]), ints([b[1] for b in blocks])))
+        assert torch.equal(again, got) and status.item() == 0

@@ -22,6 +22,10 @@ def test_plan_step_packs_sequences_and_lists_query_tiles():
     keys = [arrays["seq_kv_len"][s] - arrays["seq_q_len"][s] + f for s, f in tiles]
     assert keys == sorted(keys, reverse=True)
     assert all(a.dtype == np.int32 for a in arrays.values())
+    # the same list in blocks of 256 queries (what the tensor-core prompt attention launches)
+    more = plan_step([StepEntry(0, list(range(600)), []), StepEntry(1, list(range(100)), [])], [0, 300], 1000)
+    blocks = list(zip(more["block_seq"].tolist(), more["block_first"].tolist()))
+    assert blocks == [(0, 512), (1, 0), (0, 256), (0, 0)]      # most keys first: 512, 300, 256, 0 before them
 
 
 @pytest.mark.parametrize("entries,starts,message", [
