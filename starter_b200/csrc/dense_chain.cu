@@ -30,8 +30,6 @@
 // the SM count), which is what makes waiting for each other legal.  Every wait (on an mbarrier, on
 // the grid counter) gives up after a time limit, raises bit 32 of *status and a flag in the sync
 // area that makes all other CTAs (and later launches, until the host clears it) give up at once.
-#include <stdlib.h>
-
 #include "tcgen05.cuh"
 
 #define DC_TILE_N 128
@@ -180,16 +178,11 @@ struct DcShared {
 };
 
 template <int BM>
-__global__ void __launch_bounds__(DC_THREADS, 3)
+__global__ void __launch_bounds__(DC_THREADS, 1)
 dense_chain_kernel(const __grid_constant__ DcMaps maps, const __grid_constant__ DcParams p) {
   constexpr int X_BYTES = BM * DC_TILE_K * 2;
   constexpr int SLOT_BYTES = DC_W_BYTES + X_BYTES;
-  // A k-block is four MMAs of 16 in k.  Adding all four into one accumulator makes each wait for the
-  // one before it (a few hundred cycles each with so few columns), and with one CTA per SM nothing
-  // else keeps the tensor core busy meanwhile: the chain of dependent MMAs, not memory, would set
-  // the pace.  So the four go to NACC accumulators of their own, which are added on the way out.
-  constexpr int NACC = BM <= 32 ? 4 : 2;
-  constexpr uint32_t TMEM_COLS = 2 * NACC * BM < 32 ? 32 : 2 * NACC * BM;
+  constexpr uint32_t TMEM_COLS = 2 * BM < 32 ? 32 : 2 * BM;   // two accumulators in turn
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* ring = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -290,7 +283,7 @@ dense_chain_kernel(const __grid_constant__ DcMaps maps, const __grid_constant__ 
           }
           if (use >= 2 && !mbar_wait(&sh.acc_empty[a], ((use >> 1) - 1) & 1, abort, limit)) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t acc = tmem + (uint32_t)(a * NACC * BM);
+          const uint32_t acc = tmem + (uint32_t)(a * BM);
           for (int kb = k0; kb < k1; ++kb, ++i) {
             const int slot = i % SLOTS;
             if (!mbar_wait(&sh.full[slot], (i / SLOTS) & 1, abort, limit)) break;
@@ -299,8 +292,7 @@ dense_chain_kernel(const __grid_constant__ DcMaps maps, const __grid_constant__ 
             const uint64_t a_desc = smem_desc(a_addr), b_desc = smem_desc(a_addr + DC_W_BYTES);
 #pragma unroll
             for (int k = 0; k < DC_TILE_K / 16; ++k)
-              umma_bf16(acc + (uint32_t)((k % NACC) * BM), a_desc + 2 * k, b_desc + 2 * k, idesc,
-                        (kb > k0 || k >= NACC) ? 1u : 0u);
+              umma_bf16(acc, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > k0 || k > 0) ? 1u : 0u);
             umma_commit(&sh.empty[slot]);
           }
           if (*abort) break;
@@ -512,14 +504,7 @@ dense_chain_kernel(const __grid_constant__ DcMaps maps, const __grid_constant__ 
 #pragma unroll 1
         for (int c = 0; c < rows_pad; c += 8) {
           float v[8];
-          tmem_load8(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(a * NACC * BM + c), v);
-#pragma unroll
-          for (int q = 1; q < NACC; ++q) {
-            float more[8];
-            tmem_load8(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)((a * NACC + q) * BM + c), more);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] += more[j];
-          }
+          tmem_load8(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(a * BM + c), v);
 #pragma unroll
           for (int j = 0; j < 8; ++j)
             if (c + j < rows) dst[(size_t)(c + j) * DC_TILE_N] = v[j];
@@ -598,17 +583,14 @@ static int dc_sm_count() {
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 0;
   if (!count[device]) cudaDeviceGetAttribute(&count[device], cudaDevAttrMultiProcessorCount, device);
-  const char* e = getenv("SB_CHAIN_PER_SM");
-  return count[device] * (e && atoi(e) >= 2 ? atoi(e) : 1);
+  return count[device];
 }
 
 template <int BM>
 static int dc_launch(const DcMaps& maps, DcParams& params, int grid, cudaStream_t s) {
   constexpr int SLOT_BYTES = DC_W_BYTES + BM * DC_TILE_K * 2;
   const int norm_bytes = params.norm_floats * 4;
-  static int per_sm = 0;
-  if (!per_sm) { const char* e = getenv("SB_CHAIN_PER_SM"); per_sm = e ? atoi(e) : 1; }
-  int slots = ((per_sm == 3 ? 74 : per_sm == 2 ? 112 : 225) * 1024 - 1024 - norm_bytes) / SLOT_BYTES;   // 227 KB per CTA, less the static part
+  int slots = (225 * 1024 - 1024 - norm_bytes) / SLOT_BYTES;   // 227 KB per CTA, less the static part
   if (slots > DC_MAX_SLOTS) slots = DC_MAX_SLOTS;
   if (slots < 2) return -2;
   params.slots = slots;
