@@ -160,7 +160,7 @@ def per_stage(model, runner, slots, batch, peak_gbs, out=sys.stderr):
         return ops.attention_decode_qkv(qkv, keys, values, cache.block_table, seq_slot, kv_len, mixer.num_heads,
                                         mixer.num_kv_heads, mixer.head_dim, mixer.scale, mixer.window, m.q_norm,
                                         m.k_norm, mixer.qk_norm_eps, rot.cos, rot.sin, write_cache=True,
-                                        kv_hint=kv_tokens)
+                                        kv_hint=kv_tokens, early=True)
 
     nbytes = lambda t: t.numel() * t.element_size()
     kv_bytes = cache.bytes_per_token() // len(set(entries)) * int(kv_len.sum())

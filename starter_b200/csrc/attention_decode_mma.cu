@@ -88,6 +88,7 @@ struct FusedRope {
   const void* k_gain;
   const float* cos_table;       // [positions, D / 2]; may be null: no rotation
   const float* sin_table;
+  int early;                    // lengths and older cache pages may be read before the wait (see below)
 };
 
 template <int D, bool CLUSTER, bool FUSED>
@@ -152,7 +153,16 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out,
       }
     }
   }
-  pdl_wait();
+  // EARLY (fr.early): the caller vouches that the step's first kernel was an ordinary launch, so
+  // whatever earlier steps wrote (the row's length, every cached key and value but this step's own,
+  // which this very kernel makes) was complete before any kernel of this step started, and that no
+  // other kernel of this step writes them.  Then the length, the page numbers and the rotation
+  // table's row do not wait for the q/k/v product: two dependent loads less between the wait and the
+  // first page's copy.  (The copies themselves stay behind the wait: issued before it they were
+  // another 0.3 % faster, but the first layer of a captured step then computed on a q/k/v row that
+  // was not there yet; the cause was not found.)
+  const bool early = FUSED && fr.early;
+  if (!early) pdl_wait();
   __syncthreads();                                     // the page table is in shared memory
   const int kv_len = row_kv_len[row];
   int first = 0;
@@ -190,6 +200,7 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out,
     cp_commit();
   };
   auto load_page = [&](int i) { copy_page(i, i < n_pages ? pages[p_begin + i] : 0); };
+  if (early) pdl_wait();                               // from here on: the copies, and what the q/k/v product wrote
 #pragma unroll
   for (int i = 0; i < DM_STAGES - 1; ++i) copy_page(i, first_pages[i]);
   // this thread's share of the product's row for the first pass
@@ -561,12 +572,13 @@ int sb_attention_decode_mma(const void* q, void* out, const void* k_store, const
 // the query heads and, if has_kv, behind them the key and the value heads of each row's new token
 // (position row_kv_len - 1).  Head norm (gains may be null; gain_dtype 0 float, 1 bfloat16), rotation
 // (tables [positions, head_dim / 2] float, may be null) and, if has_kv, the cache write happen here.
+// early: see the kernel (only with has_kv: a layer that reads another layer's cache must wait).
 int sb_attention_decode_mma_fused(const void* qkv, int q_stride, void* out, void* k_store, void* v_store,
                                   const int* block_table, int table_stride, const int* row_slot,
                                   const int* row_kv_len, int rows, int heads, int kv_heads, int head_dim,
                                   float scale, int window, int n_splits, float* part_acc, float* part_ml,
                                   const void* q_gain, const void* k_gain, int gain_dtype, float eps,
-                                  const float* cos_table, const float* sin_table, int has_kv,
+                                  const float* cos_table, const float* sin_table, int has_kv, int early,
                                   cudaStream_t s) {
   if (rows == 0) return 0;
   if (kv_heads <= 0 || heads % kv_heads || n_splits < 1) return -2;
@@ -575,6 +587,7 @@ int sb_attention_decode_mma_fused(const void* qkv, int q_stride, void* out, void
   FusedRope fr;
   fr.q_stride = q_stride; fr.has_kv = has_kv; fr.gain_f32 = gain_dtype == 0; fr.eps = eps;
   fr.q_gain = q_gain; fr.k_gain = k_gain; fr.cos_table = cos_table; fr.sin_table = sin_table;
+  fr.early = early && has_kv;
 #define ARGS qkv, out, k_store, v_store, block_table, table_stride, row_slot, row_kv_len, rows, heads, \
              kv_heads, scale, window, n_splits, part_acc, part_ml, fr, s
   switch (head_dim) {

@@ -260,9 +260,19 @@ extern "C" {
 
 // dtype: 0 float, 1 bfloat16.  gain_dtype likewise.
 int sb_embedding(int dtype, const int* tokens, const void* table, void* out, int n_tokens, int hidden,
-                 int vocab, int* status, cudaStream_t s) {
+                 int vocab, int* status, int serial, cudaStream_t s) {
   if (n_tokens == 0) return 0;
   const int threads = hidden >= 1024 ? 256 : 128;
+  if (serial) {
+    // An ordinary launch: it starts only when everything before it on the stream has completed.  As
+    // the first kernel of a step it is the fence behind which later kernels of the step may read,
+    // before their own dependent-launch wait, whatever earlier steps wrote.
+    if (dtype == 0)
+      embedding_kernel<float><<<n_tokens, threads, 0, s>>>(tokens, (const float*)table, (float*)out, hidden, vocab, status);
+    else
+      embedding_kernel<bf16><<<n_tokens, threads, 0, s>>>(tokens, (const bf16*)table, (bf16*)out, hidden, vocab, status);
+    return SB_LAUNCH_RESULT();
+  }
   if (dtype == 0)
     return launch_dependent(embedding_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, tokens, (const float*)table, (float*)out, hidden, vocab, status);
   return launch_dependent(embedding_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, s, tokens, (const bf16*)table, (bf16*)out, hidden, vocab, status);

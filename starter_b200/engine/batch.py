@@ -59,6 +59,10 @@ class StepContext:
     #: from the device arrays above alone (every sequence then brings exactly one token, row ``i``
     #: belongs to ``seq_slot[i]``)
     host: dict
+    #: True once the step's first kernel has run as an ordinary (not dependent) launch: everything
+    #: earlier steps wrote is then complete before any kernel of this step starts, and a kernel may
+    #: read it before its own dependent-launch wait.  Set by the model; False for a context made by hand.
+    fenced: bool = False
 
     @property
     def is_decode(self) -> bool:

@@ -149,7 +149,10 @@ class DecoderModel:
 
     def hidden(self, ctx):
         """Run the layers; returns ``(residual, pending)`` with the last sum still open."""
-        residual = ops.embedding(ctx.tokens, self.embed, ctx.status)
+        # the step's first kernel is an ordinary launch: the fence behind which the step's other
+        # kernels may read early what earlier steps left (lengths, cache pages)
+        residual = ops.embedding(ctx.tokens, self.embed, ctx.status, fence=True)
+        ctx.fenced = True
         pending = None
         for entry in self.spec.schedule:
             residual, pending = self.blocks[entry.layer](residual, pending, ctx, entry.cache,

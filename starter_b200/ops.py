@@ -73,6 +73,8 @@ def _need(t, name, dtype=None, ndim=None):
 
 #: how many kernels of this library have been launched by this process (library GEMMs not counted)
 launch_count = 0
+#: switch for the decode attention's reads before its dependent-launch wait (see attention_decode_qkv)
+EARLY_READS = True
 
 
 def _check(rc, what, kernels=1):
@@ -96,14 +98,18 @@ def _gain_code(x, gain):
 
 # ---------------------------------------------------------------------------------------- rows
 
-def embedding(tokens, table, status=None):
-    """``out[t] = table[tokens[t]]``; ``tokens`` int32 ``[T]``, ``table`` ``[V, H]``."""
+def embedding(tokens, table, status=None, fence=False):
+    """``out[t] = table[tokens[t]]``; ``tokens`` int32 ``[T]``, ``table`` ``[V, H]``.
+
+    ``fence``: launch it as an ordinary kernel (not a dependent launch), so that it starts only when
+    everything before it on the stream has completed.  As a step's first kernel it is what lets later
+    kernels of the step read, before their own dependent-launch wait, what earlier steps wrote."""
     _need(tokens, "tokens", torch.int32, 1)
     _need(table, "table", None, 2)
     out = torch.empty((tokens.shape[0], table.shape[1]), dtype=table.dtype, device=table.device)
     rc = _lib("elementwise").sb_embedding(
         _code(table.dtype), _ptr(tokens), _ptr(table), _ptr(out), tokens.shape[0], table.shape[1],
-        table.shape[0], _ptr(status), _stream())
+        table.shape[0], _ptr(status), int(fence), _stream())
     _check(rc, "embedding")
     return out
 
@@ -466,11 +472,16 @@ def decode_from_qkv_takes(head_dim: int, dtype) -> bool:
 
 def attention_decode_qkv(qkv, k_store, v_store, block_table, row_slot, row_kv_len, heads, kv_heads, head_dim,
                          scale, window, q_gain, k_gain, eps, cos_table, sin_table, write_cache=True,
-                         n_splits=None, kv_hint=0):
+                         n_splits=None, kv_hint=0, early=False):
     """One-token attention straight from the q/k/v product (bfloat16, tensor cores): head norm,
     rotation and the cache write of ``qk_norm_rope_store`` happen inside the attention kernel, with
     the same arithmetic.  Row ``i`` of ``qkv`` is the new token of the sequence in ``row_slot[i]``, at
-    position ``row_kv_len[i] - 1``.  ``qkv`` holds the queries alone when ``write_cache`` is false."""
+    position ``row_kv_len[i] - 1``.  ``qkv`` holds the queries alone when ``write_cache`` is false.
+
+    ``early``: the caller vouches that ``row_kv_len``, the page table and every cached key and value
+    but the new token's were complete before this step's first kernel started (``embedding(...,
+    fence=True)``) and that nothing else in this step writes them; the kernel then reads the lengths
+    and the page numbers before its dependent-launch wait, while the q/k/v product still runs."""
     _need(qkv, "qkv", torch.bfloat16, 2)
     if not decode_from_qkv_takes(head_dim, qkv.dtype):
         raise KernelError(f"head_dim {head_dim} is not one of {PREFILL_HEAD_DIMS}")
@@ -514,7 +525,7 @@ def attention_decode_qkv(qkv, k_store, v_store, block_table, row_slot, row_kv_le
         block_table.shape[1], _ptr(row_slot), _ptr(row_kv_len), rows, heads, kv_heads, head_dim,
         ctypes.c_float(scale), int(window or 0), n_splits, _ptr(part_acc), _ptr(part_ml), _ptr(q_gain),
         _ptr(k_gain), gain_code, ctypes.c_float(eps), _ptr(cos_table), _ptr(sin_table), int(write_cache),
-        _stream())
+        int(bool(early) and write_cache and EARLY_READS), _stream())
     _check(rc, "attention_decode_fused", 2 if n_splits > 1 and not in_cluster else 1)
     return out
 

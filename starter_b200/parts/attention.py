@@ -85,7 +85,9 @@ class GroupedQueryAttention(Part):
             a = ops.attention_decode_qkv(qkv, keys, values, cache.block_table, ctx.seq_slot, ctx.seq_kv_len,
                                          s.num_heads, s.num_kv_heads, s.head_dim, s.scale, s.window,
                                          self.q_norm, self.k_norm, s.qk_norm_eps, cos, sin,
-                                         write_cache=writes_cache, kv_hint=ctx.max_kv_len)
+                                         write_cache=writes_cache, kv_hint=ctx.max_kv_len,
+                                         # this layer alone writes the pages it reads in this step
+                                         early=ctx.fenced and writes_cache)
             return ops.linear(a, self.o, status=ctx.status)
         q = ops.qk_norm_rope_store(
             qkv, s.num_heads, s.num_kv_heads, s.head_dim, self.q_norm, self.k_norm, s.qk_norm_eps,
