@@ -136,7 +136,7 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out,
   }
   constexpr int L = D / 16, HALF = D / 2, PER_PASS = DM_THREADS / L;
   const int part = tid % L;
-  const bf16* in_row = FUSED ? q + (size_t)row * fr.q_stride : nullptr;
+  const bf16* in_row = FUSED ? q + (size_t)row * fr.q_stride : nullptr;   // laundered after the wait, see there
   // the item of a pass: 0..15 are the tile's query heads, 16 is the new key (FUSED)
   auto item_source = [&](int item) {
     return in_row + (size_t)(item == DM_ROWS ? heads + kvh : kvh * groups + g0 + item) * D + part * 8;
@@ -156,13 +156,15 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out,
   // EARLY (fr.early): the caller vouches that the step's first kernel was an ordinary launch, so
   // whatever earlier steps wrote (the row's length, every cached key and value but this step's own,
   // which this very kernel makes) was complete before any kernel of this step started, and that no
-  // other kernel of this step writes them.  Then the length, the page numbers and the rotation
-  // table's row do not wait for the q/k/v product: two dependent loads less between the wait and the
-  // first page's copy.  (The copies themselves stay behind the wait: issued before it they were
-  // another 0.3 % faster, but the first layer of a captured step then computed on a q/k/v row that
-  // was not there yet; the cause was not found.)
+  // other kernel of this step writes them.  Then the length, the page numbers, the rotation table's
+  // row and the first pages' copies do not wait for the q/k/v product: they are under way while it
+  // still runs.  What the product wrote is read behind the wait, through laundered pointers
+  // (SB_BEHIND_WAIT: without them the compiler moved the q/k/v row's loads up among the copies).
   const bool early = FUSED && fr.early;
-  if (!early) pdl_wait();
+  if (!early) {
+    pdl_wait();
+    SB_BEHIND_WAIT(row_kv_len);                        // the step before's sampling kernel advances it
+  }
   __syncthreads();                                     // the page table is in shared memory
   const int kv_len = row_kv_len[row];
   int first = 0;
@@ -200,9 +202,11 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out,
     cp_commit();
   };
   auto load_page = [&](int i) { copy_page(i, i < n_pages ? pages[p_begin + i] : 0); };
-  if (early) pdl_wait();                               // from here on: the copies, and what the q/k/v product wrote
 #pragma unroll
   for (int i = 0; i < DM_STAGES - 1; ++i) copy_page(i, first_pages[i]);
+  if (early) pdl_wait();                               // from here on: what the q/k/v product wrote
+  SB_BEHIND_WAIT(in_row);
+  SB_BEHIND_WAIT(q);
   // this thread's share of the product's row for the first pass
   uint4 raw_lo0 = make_uint4(0, 0, 0, 0), raw_hi0 = make_uint4(0, 0, 0, 0);
   if (FUSED && item_loadable(tid / L)) {
@@ -484,6 +488,8 @@ __global__ void attention_merge_mma_kernel(const float* __restrict__ part_acc,
                                            int n_splits, int head_dim) {
   pdl_trigger();
   pdl_wait();
+  SB_BEHIND_WAIT(part_acc);
+  SB_BEHIND_WAIT(part_ml);
   const size_t rh = blockIdx.x;
   float m_all = -INFINITY;
   for (int s = 0; s < n_splits; ++s) m_all = fmaxf(m_all, part_ml[(rh * n_splits + s) * 2]);

@@ -71,6 +71,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out,
 
   pdl_trigger();
   pdl_wait();
+  SB_BEHIND_WAIT(q);
   const int tile = blockIdx.x, head = blockIdx.y;
   const int seq = tile_seq[tile];
   const int q_first = tile_first[tile];         // first query of this tile within the step's tokens of seq

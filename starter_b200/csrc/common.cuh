@@ -94,6 +94,15 @@ __device__ __forceinline__ size_t page_row(int page, int head, int offset, int k
 // buffer may be recycled memory that an earlier kernel still reads).  Because a kernel cannot
 // complete before its own pdl_wait() returns, completion is transitive along the stream.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// A load through a `const T* __restrict__` parameter counts as invariant (nothing in the kernel can
+// change what it reads), so the compiler is free to move it up, across volatile asm and its memory
+// clobber too: across pdl_wait().  Then the kernel reads what its predecessor has not written yet.
+// (Seen once: the decode attention's first layer in a captured step read its q/k/v row early.)
+// SB_BEHIND_WAIT(p), placed after pdl_wait(), hands the compiler the pointer back as a value it
+// has not seen before; every load through it depends on that value and stays behind the wait.
+// It goes on every parameter an earlier kernel of the stream may have written and that this
+// kernel reads with ordinary loads (copies issued by inline asm keep their place by themselves).
+#define SB_BEHIND_WAIT(p) asm volatile("" : "+l"(p) : : "memory")
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // The same, as thread-block clusters of `cluster` CTAs (every grid dimension a multiple of it).

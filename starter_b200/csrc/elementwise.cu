@@ -13,6 +13,7 @@ __global__ void embedding_kernel(const int* __restrict__ tokens, const T* __rest
                                  T* __restrict__ out, int hidden, int vocab, int* status) {
   pdl_trigger();
   pdl_wait();
+  SB_BEHIND_WAIT(tokens);
   const int row = blockIdx.x;
   int tok = tokens[row];
   const bool bad = tok < 0 || tok >= vocab;
@@ -37,6 +38,8 @@ __global__ void rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delta,
   __shared__ float scratch[33];
   pdl_trigger();
   pdl_wait();
+  SB_BEHIND_WAIT(delta);
+  SB_BEHIND_WAIT(rows);
   const int out_row = blockIdx.x;
   const int in_row = rows ? rows[out_row] : out_row;
   T* xr = x + (size_t)in_row * hidden;
@@ -131,6 +134,8 @@ __global__ void rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ delt
     }
   }
   pdl_wait();
+  SB_BEHIND_WAIT(delta);
+  SB_BEHIND_WAIT(rows);
   const int out_row = blockIdx.x;
   const int in_row = rows ? rows[out_row] : out_row;
   T* xr = x + (size_t)in_row * hidden;
@@ -215,6 +220,7 @@ template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, int inner, size_t total) {
   pdl_trigger();
   pdl_wait();
+  SB_BEHIND_WAIT(gu);
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (; i < total; i += stride) {
@@ -233,6 +239,7 @@ __global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ act,
   constexpr int N = 16 / sizeof(T);
   pdl_trigger();
   pdl_wait();
+  SB_BEHIND_WAIT(gu);
   const int per_row = inner / N;
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;

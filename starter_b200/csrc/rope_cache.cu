@@ -21,6 +21,9 @@ __global__ void qk_norm_rope_store_kernel(
     int head_dim, float eps, int heads_per_token, int row_stride) {
   pdl_trigger();
   pdl_wait();
+  SB_BEHIND_WAIT(qkv);
+  SB_BEHIND_WAIT(tok_pos);
+  SB_BEHIND_WAIT(tok_slot);
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp >= n_tokens * heads_per_token) return;
@@ -126,6 +129,9 @@ __global__ void qk_norm_rope_store_vec_kernel(
     float eps, int heads_per_token, int row_stride) {
   pdl_trigger();
   pdl_wait();
+  SB_BEHIND_WAIT(qkv);
+  SB_BEHIND_WAIT(tok_pos);
+  SB_BEHIND_WAIT(tok_slot);
   constexpr int HALF = L * 8, D = 2 * HALF;
   // grid (tokens, blocks of heads): no index needs a division
   const int token = blockIdx.x;

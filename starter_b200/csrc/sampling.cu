@@ -57,6 +57,9 @@ __global__ void sample_chunk_kernel(const float* __restrict__ logits, int vocab,
   __shared__ int sh_i[32];
   pdl_trigger();
   pdl_wait();
+  SB_BEHIND_WAIT(logits);
+  SB_BEHIND_WAIT(temperature);
+  SB_BEHIND_WAIT(request_key);
   const int row = blockIdx.y, chunk = blockIdx.x;
   const float* lr = logits + (size_t)row * row_stride;
   const float t = temperature ? temperature[row] : 0.f;
@@ -91,6 +94,8 @@ __global__ void sample_pick_kernel(const float* __restrict__ cand_v, const int* 
   __shared__ int sh_i[32];
   pdl_trigger();
   pdl_wait();
+  SB_BEHIND_WAIT(cand_v);
+  SB_BEHIND_WAIT(cand_i);
   const int row = blockIdx.x;
   Best b = {-INFINITY, 0x7fffffff};
   for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
