@@ -147,3 +147,51 @@ def test_captured_decode_is_reproducible_over_many_steps(tmp_path_factory):
     engine.runner.check_status()
     assert first == again
     assert len({tuple(step) for step in first}) > 20      # not stuck on one token
+
+
+WIDE = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=1, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8, head_dim=128,
+    intermediate_size=17408, vocab_size=1031, rope_theta=1e6, rms_norm_eps=1e-6,
+    tie_word_embeddings=False, max_position_embeddings=4096, hidden_act="silu",
+)
+
+
+def test_a_layer_of_the_widest_model_size(tmp_path_factory):
+    """Hidden 5120, 40 query heads over 8 key/value heads, intermediate 17408, an untied head (the
+    14B row of the measurement table): other tile counts, split choices and cluster sizes than the 4B
+    layer.  A prompt whole, then unequal sequences through the captured step, against the plain model."""
+    from starter_b200 import Engine
+    from starter_b200.config import config_from_dict
+    from starter_b200.engine import ModelRunner, StepEntry, load_model
+    from starter_b200.engine.generate import Request
+    from starter_b200.weights import write_model_folder
+
+    folder = write_model_folder(str(tmp_path_factory.mktemp("wide")), config_from_dict(WIDE), 5, torch.bfloat16)
+    cfg, w = plain.read_model_folder(folder)
+    vocab = cfg["vocab_size"]
+    runner = ModelRunner(load_model(folder, "bfloat16"), max_tokens=64 * 8, max_sequences=4)
+    seq = random_prompt(150, vocab, 21)
+    slot = runner.open_sequence()
+    got = runner.step([StepEntry(slot, seq, list(range(150)))])
+    runner.close_sequence(slot)
+    assert_close(got, plain.plain_forward(cfg, w, seq), "bfloat16", "widest layer, 150 tokens whole")
+    runner.check_status()
+    del runner
+    prompts = [random_prompt(n, vocab, 30 + n) for n in (70, 9, 1)]
+    engine = Engine(folder, dtype="bfloat16", max_batch=4)
+    requests = [Request(list(p), 5) for p in prompts]
+    loop = engine._ensure_room(requests, len(requests))
+    loop.lookahead = False            # each step's logits are read before the next step runs
+    graphs = engine.runner.graphs
+    tokens, rows = [[] for _ in prompts], []
+    for n, step_out in enumerate(loop.stream_batch(requests)):
+        if n > 0:
+            rows.append(graphs.logits[graphs.last_key].clone())
+        for i in range(3):
+            tokens[i].append(step_out[i])
+    engine.runner.check_status()
+    want = [plain.plain_forward(cfg, w, list(p) + t) for p, t in zip(prompts, tokens)]
+    for step, got in enumerate(rows):
+        ref = torch.stack([want[i][len(prompts[i]) + step] for i in range(3)])
+        assert_close(got, ref, "bfloat16", f"widest layer, captured step {step}")
