@@ -55,13 +55,14 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort,
+                                          uint64_t limit_ns = WAIT_LIMIT_NS) {
   if (mbar_try(bar, parity)) return true;
   const uint64_t start = now_ns();
   while (true) {
     if (mbar_try(bar, parity)) return true;
     if (*abort) return false;
-    if (now_ns() - start > WAIT_LIMIT_NS) { *abort = 1; return false; }
+    if (now_ns() - start > limit_ns) { *abort = 1; return false; }
   }
 }
 
@@ -106,7 +107,8 @@ attention_decode_kernel(const T* __restrict__ q, T* __restrict__ out, const T* _
                         int table_stride, const int* __restrict__ row_slot,
                         const int* __restrict__ row_kv_len, int heads, int kv_heads, float scale_log2,
                         int window, int n_splits, float* __restrict__ part_acc,
-                        float* __restrict__ part_ml, int* status) {
+                        float* __restrict__ part_ml, int* status, unsigned long long limit_ns,
+                        int withhold_page) {
   using Shape = DecodeShape<T, D>;
   constexpr int LPK = D / AD_ELEMS;  // lanes that share a key
   constexpr int KPW = 32 / LPK;      // keys a warp takes at a time
@@ -153,18 +155,20 @@ attention_decode_kernel(const T* __restrict__ q, T* __restrict__ out, const T* _
       int issued = 0;
       for (int i = 0; i < n_pages; ++i) {
         const int s = i % STAGES;
-        if (i >= STAGES && !mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, abort)) break;
+        if (i >= STAGES && !mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, abort, limit_ns)) break;
         const size_t base = page_row(pages[p_begin + i], kvh, 0, kv_heads, D);
         uint8_t* dst = ring + (size_t)s * Shape::STAGE_BYTES;
         mbar_expect_tx(&full_bar[s], Shape::STAGE_BYTES);
         bulk_load(dst, k_store + base, Shape::PAGE_BYTES, &full_bar[s]);
-        bulk_load(dst + Shape::PAGE_BYTES, v_store + base, Shape::PAGE_BYTES, &full_bar[s]);
+        // (tests of the give-up path leave one page's values out: its stage then never completes)
+        if (i != withhold_page)
+          bulk_load(dst + Shape::PAGE_BYTES, v_store + base, Shape::PAGE_BYTES, &full_bar[s]);
         issued = i + 1;
       }
       if (*abort) {
         for (int i = max(issued - STAGES, 0); i < issued; ++i) {
           const uint64_t start = now_ns();
-          while (!mbar_try(&full_bar[i % STAGES], (i / STAGES) & 1) && now_ns() - start < WAIT_LIMIT_NS) {}
+          while (!mbar_try(&full_bar[i % STAGES], (i / STAGES) & 1) && now_ns() - start < limit_ns) {}
         }
       }
     }
@@ -189,7 +193,7 @@ attention_decode_kernel(const T* __restrict__ q, T* __restrict__ out, const T* _
 
     for (int i = 0; i < n_pages; ++i) {
       const int s = i % STAGES;
-      if (!mbar_wait(&full_bar[s], (i / STAGES) & 1, abort)) break;
+      if (!mbar_wait(&full_bar[s], (i / STAGES) & 1, abort, limit_ns)) break;
       const T* kp = reinterpret_cast<const T*>(ring + (size_t)s * Shape::STAGE_BYTES);
       const T* vp = reinterpret_cast<const T*>(ring + (size_t)s * Shape::STAGE_BYTES + Shape::PAGE_BYTES);
       const int p = p_begin + i;
@@ -301,6 +305,10 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_acc,
   }
 }
 
+// Set by sb_attention_decode_withhold for the next launch only (tests of the give-up path).
+static unsigned long long next_limit_ns = WAIT_LIMIT_NS;
+static int next_withhold_page = -1;
+
 template <typename T, int D>
 static int launch(const void* q, void* out, const void* k_store, const void* v_store,
                   const int* block_table, int table_stride, const int* row_slot, const int* row_kv_len,
@@ -320,7 +328,9 @@ static int launch(const void* q, void* out, const void* k_store, const void* v_s
   attention_decode_kernel<T, D><<<grid, AD_THREADS, Shape::RING_BYTES, s>>>(
       (const T*)q, (T*)out, (const T*)k_store, (const T*)v_store, block_table, table_stride, row_slot,
       row_kv_len, heads, kv_heads, scale * 1.4426950408889634f, window, n_splits, part_acc, part_ml,
-      status);
+      status, next_limit_ns, next_withhold_page);
+  next_limit_ns = WAIT_LIMIT_NS;
+  next_withhold_page = -1;
   int rc = SB_LAUNCH_RESULT();
   if (rc || n_splits == 1) return rc;
   attention_merge_kernel<T><<<rows * heads, D < 128 ? D : 128, 0, s>>>(part_acc, part_ml, (T*)out,
@@ -329,6 +339,14 @@ static int launch(const void* q, void* out, const void* k_store, const void* v_s
 }
 
 extern "C" {
+
+// For tests of the give-up path: the NEXT sb_attention_decode launch leaves out the values of page
+// `page` of every block's range (blocks with fewer pages are unaffected) and its waits give up after
+// `limit_ns`.  That launch cannot finish its sums; it must return with bit 8 of *status set.
+void sb_attention_decode_withhold(int page, unsigned long long limit_ns) {
+  next_withhold_page = page;
+  next_limit_ns = limit_ns ? limit_ns : WAIT_LIMIT_NS;
+}
 
 // q, out: [rows, heads * head_dim]; one query per row at position row_kv_len[row] - 1 of the sequence
 // in slot row_slot[row].  part_acc [rows * heads * n_splits * head_dim] and part_ml

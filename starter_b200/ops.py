@@ -531,11 +531,15 @@ def attention_decode_qkv(qkv, k_store, v_store, block_table, row_slot, row_kv_le
 
 
 def attention_decode(q, k_store, v_store, block_table, row_slot, row_kv_len, heads, kv_heads, head_dim,
-                     scale, window=None, n_splits=None, status=None, kv_hint=0):
+                     scale, window=None, n_splits=None, status=None, kv_hint=0, withhold=None):
     """One query per row (the newest token of its sequence) over that sequence's cached keys.
 
     ``row_kv_len[r]`` is the sequence's length with the query's own key already filed; the lengths
-    stay on the device.  ``head_dim`` must be one of ``DECODE_HEAD_DIMS``."""
+    stay on the device.  ``head_dim`` must be one of ``DECODE_HEAD_DIMS``.
+
+    ``withhold = (page, limit_ns)`` is for tests of the CUDA-core kernel's give-up path: the values of
+    that page of every block's range are not copied, the wait on them runs out after ``limit_ns``,
+    the kernel returns with bit 8 of ``status`` set and the result is undefined."""
     _need(q, "q", None, 2)
     rows = q.shape[0]
     if q.shape[1] != heads * head_dim:
@@ -569,6 +573,8 @@ def attention_decode(q, k_store, v_store, block_table, row_slot, row_kv_len, hea
             _ptr(row_slot), _ptr(row_kv_len), rows, heads, kv_heads, head_dim, ctypes.c_float(scale),
             int(window or 0), n_splits, _ptr(part_acc), _ptr(part_ml), _stream())
     else:
+        if withhold is not None:
+            _lib("attention_decode").sb_attention_decode_withhold(int(withhold[0]), ctypes.c_ulonglong(int(withhold[1])))
         rc = _lib("attention_decode").sb_attention_decode(
             _code(q.dtype), _ptr(q), _ptr(out), _ptr(k_store), _ptr(v_store), _ptr(block_table),
             block_table.shape[1], _ptr(row_slot), _ptr(row_kv_len), rows, heads, kv_heads, head_dim,

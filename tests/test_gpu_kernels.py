@@ -339,6 +339,31 @@ def test_tensor_core_product(rows, n, k, gated, bm, splits):
     assert status.item() == 0
 
 
+def test_a_wait_in_the_decode_attention_that_runs_out_is_reported():
+    """The CUDA-core decode attention (the float32 path's) with one page's values left out on purpose:
+    the wait on that page gives up after 2 ms, the kernel returns, bit 8 of the status word is set; the
+    same call without the gap is right afterwards."""
+    from starter_b200 import ops
+    from starter_b200.engine.runner import ModelRunner
+
+    heads, kv_heads, d = 4, 2, 32
+    lengths = [200, 130]
+    c = attention_case("float32", heads, kv_heads, d, lengths=lengths, new=[1, 1], window=None, seed=77)
+    status = dev(torch.zeros(1, dtype=torch.int32))
+    args = (dev(c["q"]), dev(c["ks"]), dev(c["vs"]), dev(c["table"]), dev(c["slot"]),
+            dev(torch.tensor(lengths, dtype=torch.int32)), heads, kv_heads, d, c["scale"], None)
+    ops.attention_decode(*args, n_splits=1, status=status, withhold=(1, 2_000_000))
+    torch.cuda.synchronize()
+    assert status.item() == 8
+    holder = ModelRunner.__new__(ModelRunner)
+    holder.status = status
+    with pytest.raises(RuntimeError, match="decode attention kernel ran out of time"):
+        holder.check_status()
+    got = ops.attention_decode(*args, n_splits=1, status=status)
+    assert status.item() == 0
+    assert torch.allclose(got.cpu(), c["want"], atol=2e-5, rtol=2e-5)
+
+
 @pytest.mark.parametrize("rows,n,k,gated,splits,stage", [(8, 256, 512, False, 1, 0), (8, 384, 1024, False, 4, 1),
                                                        (16, 128, 768, True, 2, 2)])
 def test_a_wait_in_the_tensor_core_product_that_runs_out_is_reported(rows, n, k, gated, splits, stage):
