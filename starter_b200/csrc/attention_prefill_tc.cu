@@ -60,17 +60,23 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
       : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
   return ok != 0;
 }
+// For tests of the give-up path (sb_attention_prefill_tc_withhold): how long a wait may take, and
+// which step's values the producer leaves out (-1: none).  Read only once a wait has spun a while.
+__device__ unsigned long long tc_wait_limit_ns = WAIT_LIMIT_NS;
+__device__ int tc_withhold_step = -1;
+
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
 #pragma unroll 1
   for (int spin = 0; spin < 2048; ++spin)
     if (mbar_try(bar, parity)) return true;
   const uint64_t start = now_ns();
+  const uint64_t limit = *(volatile unsigned long long*)&tc_wait_limit_ns;
 #pragma unroll 1
   for (uint32_t spin = 0;; ++spin) {
     if (mbar_try(bar, parity)) return true;
     if ((spin & 63) == 0) {
       if (*abort) return false;
-      if (now_ns() - start > WAIT_LIMIT_NS) { *abort = 1; return false; }
+      if (now_ns() - start > limit) { *abort = 1; return false; }
     }
   }
 }
@@ -274,7 +280,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int b = is_v ? 2 : (i & 1), use = is_v ? i : (i >> 1);
         if (use > 0 && !mbar_wait(&empty[b], (use - 1) & 1, abort)) return false;
         mbar_expect_tx(&full[b], KV_BYTES);
-        for (int half = 0; half < 2; ++half) {
+        const bool withheld = is_v && i == *(volatile int*)&tc_withhold_step;   // tests only
+        for (int half = 0; half < (withheld ? 1 : 2); ++half) {
           const int page = pages[min(page_lo + 2 * i + half, page_hi)];
           const int row = (page * kv_heads + kvh) * SB_PAGE_TOKENS;
           for (int c = 0; c < DC; ++c)
@@ -573,7 +580,19 @@ static int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMa
                           list_of_blocks);
 }
 
+static unsigned long long next_limit_ns = WAIT_LIMIT_NS;
+static int next_withhold_step = -1;
+
 extern "C" {
+
+// For tests of the give-up path: the NEXT sb_attention_prefill_tc launch leaves out half of the
+// values of step `step` (128 keys) of every block and its waits give up after `limit_ns`.  The
+// blocks cannot finish; the launch must return with bit 16 of *status set.  The switches are set
+// and put back by copies on the launch's stream, around that one launch.
+void sb_attention_prefill_tc_withhold(int step, unsigned long long limit_ns) {
+  next_withhold_step = step;
+  next_limit_ns = limit_ns ? limit_ns : WAIT_LIMIT_NS;
+}
 
 // Same contract as sb_attention_prefill; n_tokens rows in q/out, n_pages pages in the stores.
 // list_of_blocks: tile_seq/tile_first list blocks of 256 queries (else tiles of 64, see the kernel).
@@ -598,8 +617,22 @@ int sb_attention_prefill_tc(const void* q, void* out, const void* k_store, const
   if (rc) return rc;
 #define ARGS mq, mk, mv, out, block_table, table_stride, seq_slot, seq_q_start, seq_q_len, seq_kv_len, \
              tile_seq, tile_first, n_tiles, heads, kv_heads, scale, window, status, list_of_blocks, s
-  if (head_dim == 64) return launch<64>(ARGS);
-  return launch<128>(ARGS);
+  const bool test_run = next_withhold_step >= 0;
+  if (test_run) {
+    cudaMemcpyToSymbolAsync(tc_withhold_step, &next_withhold_step, sizeof(int), 0, cudaMemcpyHostToDevice, s);
+    cudaMemcpyToSymbolAsync(tc_wait_limit_ns, &next_limit_ns, sizeof(next_limit_ns), 0, cudaMemcpyHostToDevice, s);
+    cudaStreamSynchronize(s);
+  }
+  rc = head_dim == 64 ? launch<64>(ARGS) : launch<128>(ARGS);
+  if (test_run) {
+    cudaStreamSynchronize(s);
+    next_withhold_step = -1;
+    next_limit_ns = WAIT_LIMIT_NS;
+    cudaMemcpyToSymbolAsync(tc_withhold_step, &next_withhold_step, sizeof(int), 0, cudaMemcpyHostToDevice, s);
+    cudaMemcpyToSymbolAsync(tc_wait_limit_ns, &next_limit_ns, sizeof(next_limit_ns), 0, cudaMemcpyHostToDevice, s);
+    cudaStreamSynchronize(s);
+  }
+  return rc;
 #undef ARGS
 }
 

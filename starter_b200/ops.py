@@ -376,7 +376,7 @@ PREFILL_HEAD_DIMS = (16, 32, 64, 128)
 
 def attention_prefill(q, k_store, v_store, block_table, seq_slot, seq_q_start, seq_q_len, seq_kv_len,
                       tile_seq, tile_first, heads, kv_heads, head_dim, scale, window=None, status=None,
-                      kernel=None, max_q_len=None, blocks=None):
+                      kernel=None, max_q_len=None, blocks=None, withhold=None):
     """Causal attention for steps with many tokens per sequence (bfloat16, tensor cores).
 
     ``q`` ``[T, heads * head_dim]`` packed by sequence; the ``seq_*`` arrays describe each sequence
@@ -386,7 +386,9 @@ def attention_prefill(q, k_store, v_store, block_table, seq_slot, seq_q_start, s
     the mma.sync kernel, which has the smaller blocks.  ``kernel`` ("tcgen05" or "mma") forces one.
     ``blocks = (block_seq, block_first)`` is the same work list in blocks of 256 queries, which is what
     the tcgen05 kernel launches; without it that kernel is launched once per tile of 64 and three of
-    four launches find nothing to do."""
+    four launches find nothing to do.  ``withhold = (step, limit_ns)`` is for tests of the tcgen05
+    kernel's give-up path: half of the values of that step of 128 keys are not copied, the wait on them
+    runs out after ``limit_ns``, bit 16 of ``status`` is set and the result is undefined."""
     _need(q, "q", torch.bfloat16, 2)
     if q.shape[1] != heads * head_dim:
         raise KernelError(f"q has width {q.shape[1]}, expected {heads * head_dim}")
@@ -416,6 +418,9 @@ def attention_prefill(q, k_store, v_store, block_table, seq_slot, seq_q_start, s
             for name, t in (("block_seq", blocks[0]), ("block_first", blocks[1])):
                 _need(t, name, torch.int32, 1)
         list_seq, list_first = blocks if own_list else (tile_seq, tile_first)
+        if withhold is not None:
+            _lib("attention_prefill_tc").sb_attention_prefill_tc_withhold(
+                int(withhold[0]), ctypes.c_ulonglong(int(withhold[1])))
         rc = _lib("attention_prefill_tc").sb_attention_prefill_tc(
             _ptr(q), _ptr(out), _ptr(k_store), _ptr(v_store), _ptr(block_table), block_table.shape[1],
             _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), _ptr(seq_kv_len), _ptr(list_seq),

@@ -339,6 +339,34 @@ def test_tensor_core_product(rows, n, k, gated, bm, splits):
     assert status.item() == 0
 
 
+def test_a_wait_in_the_prompt_attention_that_runs_out_is_reported():
+    """The tcgen05 prompt attention with half of one step's values left out on purpose: the wait on
+    them gives up after 2 ms, every block returns, bit 16 of the status word is set; the same call
+    without the gap is right afterwards."""
+    from starter_b200 import ops
+    from starter_b200.engine.runner import ModelRunner
+
+    heads, kv_heads, d = 4, 2, 128
+    lengths = [300, 260]
+    c = attention_case("bfloat16", heads, kv_heads, d, lengths=lengths, new=lengths, window=None, seed=88)
+    q_start = [0, lengths[0]]
+    tiles = [(i, f) for i in range(2) for f in range(0, lengths[i], 64)]
+    ints = lambda v: dev(torch.tensor(v, dtype=torch.int32))
+    status = dev(torch.zeros(1, dtype=torch.int32))
+    args = (dev(c["q"]), dev(c["ks"]), dev(c["vs"]), dev(c["table"]), ints([0, 1]), ints(q_start), ints(lengths),
+            ints(lengths), ints([t[0] for t in tiles]), ints([t[1] for t in tiles]), heads, kv_heads, d, c["scale"], None)
+    ops.attention_prefill(*args, status=status, kernel="tcgen05", withhold=(0, 2_000_000))
+    torch.cuda.synchronize()
+    assert status.item() == 16
+    holder = ModelRunner.__new__(ModelRunner)
+    holder.status = status
+    with pytest.raises(RuntimeError, match="prefill attention kernel ran out of time"):
+        holder.check_status()
+    got = ops.attention_prefill(*args, status=status, kernel="tcgen05")
+    assert status.item() == 0
+    assert torch.allclose(got.cpu().float(), c["want"].float(), atol=2e-2, rtol=2e-2)
+
+
 def test_a_wait_in_the_decode_attention_that_runs_out_is_reported():
     """The CUDA-core decode attention (the float32 path's) with one page's values left out on purpose:
     the wait on that page gives up after 2 ms, the kernel returns, bit 8 of the status word is set; the
