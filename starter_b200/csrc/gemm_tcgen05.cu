@@ -307,7 +307,25 @@ static EncodeTiledFn encode_fn() {
 }
 
 // A [rows, k] row-major bfloat16 matrix read in boxes of [box_rows x 64] with 128-byte swizzle.
+// Encoding a map costs a microsecond or two on the host, and the same matrices (every weight, and
+// activation buffers the allocator hands out again) come back step after step: the last maps are
+// kept in a small direct-mapped table keyed by everything a map is made of.
+struct MapKey {
+  const void* base;
+  long long rows;
+  int k_dim, box_rows;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rows == o.rows && k_dim == o.k_dim && box_rows == o.box_rows;
+  }
+};
+struct MapSlot { MapKey key; CUtensorMap map; bool used; };
+
 static int make_map(CUtensorMap* map, const void* base, int rows, int k_dim, int box_rows) {
+  static thread_local MapSlot cache[512];
+  const MapKey key = {base, rows, k_dim, box_rows};
+  const size_t h = (((uintptr_t)base >> 8) * 0x9E3779B97F4A7C15ull + (size_t)box_rows * 31 + (size_t)rows) >> 20;
+  MapSlot& slot = cache[h & 511];
+  if (slot.used && slot.key == key) { *map = slot.map; return 0; }
   EncodeTiledFn fn = encode_fn();
   if (!fn) return -3;
   cuuint64_t dims[2] = {(cuuint64_t)k_dim, (cuuint64_t)rows};
@@ -317,7 +335,9 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int k_dim, int
   CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims, strides, box, elem,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return rc == CUDA_SUCCESS ? 0 : -4;
+  if (rc != CUDA_SUCCESS) return -4;
+  slot.key = key; slot.map = *map; slot.used = true;
+  return 0;
 }
 
 template <int BM, bool GATED>

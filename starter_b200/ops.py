@@ -18,10 +18,11 @@ from .csrc import build
 
 SMALL_ROWS = 16
 #: Up to this many rows the bfloat16 product runs on this library's tcgen05 kernel, where it is bound
-#: by streaming the weights; beyond it (prompts) the vendor's GEMM is used, as the reference does
-#: (engine/engine.py:431-450): the one-CTA 128 x 256 tile of the own kernel reaches about 60% of
-#: that library's throughput there.
-TENSOR_CORE_MAX_ROWS = 256
+#: by streaming the weights; beyond it (prompts, longer chunks) the vendor's GEMM is used, as the
+#: reference does (engine/engine.py:431-450).  Measured on the four projections of a 2560-wide layer:
+#: 63-70 us a layer for the own kernel up to 64 rows against 64-86 for the library; 78 against 78 at
+#: 96 rows, 79 against 69 at 128 and 103 against 73 at 256 with the best plan found for each.
+TENSOR_CORE_MAX_ROWS = 64
 MAX_HEAD_DIM = 256
 
 _DT = {torch.float32: 0, torch.bfloat16: 1}
@@ -56,19 +57,35 @@ def _ptr(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
 
 
+try:                                   # the raw handle of the current stream without building objects
+    _raw_stream = torch._C._cuda_getCurrentRawStream
+    _current_device = torch._C._cuda_getDevice
+except AttributeError:                 # pragma: no cover - older or newer torch: the public way
+    _raw_stream = _current_device = None
+
+
 def _stream():
+    """The current CUDA stream as a ``void*`` (called once per launch: it has to be cheap)."""
+    if _raw_stream is not None:
+        return ctypes.c_void_p(_raw_stream(_current_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
 def _need(t, name, dtype=None, ndim=None):
+    # the common case first and in one expression: this runs several times per launch
+    try:
+        if (t.is_cuda and t.is_contiguous() and (dtype is None or t.dtype == dtype)
+                and (ndim is None or t.dim() == ndim)):
+            return
+    except AttributeError:
+        pass
     if not isinstance(t, torch.Tensor) or not t.is_cuda:
         raise KernelError(f"{name} must be a CUDA tensor (there is no CPU implementation)")
     if not t.is_contiguous():
         raise KernelError(f"{name} must be contiguous, got strides {t.stride()} for shape {tuple(t.shape)}")
     if dtype is not None and t.dtype != dtype:
         raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
-    if ndim is not None and t.dim() != ndim:
-        raise KernelError(f"{name} must have {ndim} dimensions, got shape {tuple(t.shape)}")
+    raise KernelError(f"{name} must have {ndim} dimensions, got shape {tuple(t.shape)}")
 
 
 #: how many kernels of this library have been launched by this process (library GEMMs not counted)
@@ -216,9 +233,9 @@ def gemm_plan(rows: int, n_out: int, k_dim: int, gated: bool):
     k range; how deep the ring of shared-memory stages is.
 
     With few rows the product is bound by streaming the weights: about two CTAs per SM should be
-    loading, each with some 100 KB in flight.  With many rows one CTA per SM holds a large tile."""
+    loading, each with some 100 KB in flight.  With more rows two or three CTAs per SM hold 128-row tiles."""
     bm = 16
-    while bm < rows and bm < 256:
+    while bm < rows and bm < 128:
         bm *= 2
     tiles = (n_out // 64 if gated else -(-n_out // 128)) * -(-rows // bm)
     k_blocks = -(-k_dim // 64)
@@ -238,8 +255,14 @@ def gemm_plan(rows: int, n_out: int, k_dim: int, gated: bool):
         else:
             stages, splits = 4, splits4
     else:
-        stages = max(3, min(6, (200 * 1024) // stage_bytes))
-        splits = 1 if tiles >= 100 else max(1, min(8, k_blocks // 8, 148 // tiles))
+        # measured at 96 to 256 rows: 128-row tiles, two CTAs of three stages on an SM and up to four
+        # CTAs sharing a tile's k range; when there are more tiles than such CTAs fit at once, two
+        # stages (three CTAs on an SM) and two CTAs a tile
+        slots3 = 148 * ((227 * 1024) // (3 * stage_bytes + 2048))
+        if tiles > slots3:
+            stages, splits = 2, (2 if rows <= 128 and k_blocks >= 16 else 1)
+        else:
+            stages, splits = 3, max(1, min(4, k_blocks // 8, slots3 // tiles))
     return bm, splits, stages
 
 
