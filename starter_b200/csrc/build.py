@@ -42,6 +42,7 @@ SOURCES = (
     "linear_small",
     "sgemm",
     "gemm_tcgen05",
+    "gemm_prompt_tcgen05",
     "dense_chain",
     "sampling",
 )

@@ -15,6 +15,13 @@
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
+// True in exactly one lane of the (converged) warp.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t chosen;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(chosen));
+  return chosen != 0;
+}
+
 __device__ __forceinline__ uint64_t now_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));

@@ -303,6 +303,38 @@ def linear_tensor_core(x, weight, out_float=False, gated=False, bm=None, splits=
     return out
 
 
+def linear_prompt(x, weight, gated=False, bn=0, pairs=0, status=None, withhold=None):
+    """The bfloat16 product for many rows: the persistent CTA-pair kernel (csrc/gemm_prompt_tcgen05.cu).
+
+    ``bn`` is the number of weight rows per tile (0: chosen by the kernel's host side), ``pairs`` the
+    number of CTA pairs (0: one per two SMs).  ``withhold = (k_block, limit_ns)`` is for tests of the
+    give-up path: one weight copy is left out, a wait runs out after ``limit_ns``, the kernel returns,
+    bit 4 of ``status`` is set and the result is undefined."""
+    _need(x, "x", torch.bfloat16, 2)
+    _need(weight, "weight", torch.bfloat16, 2)
+    rows, k_dim = x.shape
+    n_total = weight.shape[0]
+    n_out = n_total // 2 if gated else n_total
+    if weight.shape[1] != k_dim:
+        raise KernelError(f"weight {tuple(weight.shape)} does not take inputs of width {k_dim}")
+    if k_dim % 8 or (gated and n_total % 2) or x.data_ptr() % 16 or weight.data_ptr() % 16:
+        raise KernelError(f"the prompt product needs k % 8 == 0 and 16-byte aligned operands; got k = {k_dim}")
+    out = torch.empty((rows, n_out), dtype=torch.bfloat16, device=x.device)
+    lib = _lib("gemm_prompt_tcgen05")
+    if withhold is not None:
+        rc = lib.sb_gemm_prompt_withheld(_ptr(x), _ptr(weight), _ptr(out), rows, n_out, k_dim, int(bn), int(pairs),
+                                         int(gated), _ptr(status), ctypes.c_ulonglong(int(withhold[1])),
+                                         int(withhold[0]), _stream())
+    else:
+        rc = lib.sb_gemm_prompt(_ptr(x), _ptr(weight), _ptr(out), rows, n_out, k_dim, int(bn), int(pairs),
+                                int(gated), _ptr(status), _stream())
+    if rc in (-3, -4):
+        raise KernelError("the TMA descriptors for the prompt product could not be made "
+                          f"(code {rc}); is the driver too old for cuTensorMapEncodeTiled?")
+    _check(rc, "gemm_prompt_tcgen05")
+    return out
+
+
 # ---------------------------------------------------------------------------------------- attention
 
 def rotation_tables(rotation, head_dim: int):
