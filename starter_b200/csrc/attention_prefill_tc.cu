@@ -37,6 +37,12 @@
 #define WAIT_LIMIT_NS 2000000000ull
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+// True in exactly one lane of the (converged) warp.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t chosen;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(chosen));
+  return chosen != 0;
+}
 __device__ __forceinline__ uint64_t now_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -232,7 +238,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int pos0 = kv_len - q_len + q_first;
   const int kvh = head / (heads / kv_heads);
   const int* pages = block_table + (size_t)seq_slot[seq] * table_stride;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // the warp's number as a value the compiler knows to be the same in every lane
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
 
   const int hi = pos0 + rows_valid - 1;
   int lo = 0;
@@ -265,27 +272,31 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   volatile int* abort = &abort_flag;
 
   if (warp == 8) {
-    // ---------------- producer
-    if (lane == 0) {
+    // ---------------- producer: the whole warp walks the schedule, one elected lane issues the
+    // copies (addresses and coordinates are then the same in every lane and can live in the uniform
+    // registers the copy instructions want; run by one lane inside a branch on the lane number, each
+    // copy costs over a hundred cycles to issue)
+    {
+      const bool elected = elect_one();
       pdl_wait();
       const int q_row0 = seq_q_start[seq] + q_first;
       const int q_tiles = n_tile[1] ? 2 : 1;
-      mbar_expect_tx(&q_full, q_tiles * Q_BYTES);
+      if (elected) mbar_expect_tx(&q_full, q_tiles * Q_BYTES);
       for (int t = 0; t < q_tiles; ++t)
         for (int c = 0; c < DC; ++c)
-          tma_load_2d(q_sm + t * Q_BYTES + c * SUB, &map_q, &q_full, head * D + c * 64, q_row0 + t * TC_BQ);
+          if (elected) tma_load_2d(q_sm + t * Q_BYTES + c * SUB, &map_q, &q_full, head * D + c * 64, q_row0 + t * TC_BQ);
       // Keys alternate between buffers 0 and 1 and run a step ahead of the values, which have
       // buffer 2: K0 V0 K1 | K2 V1 | K3 V2 ...  (S of step i+1 is issued early in step i, PV late.)
       auto load = [&](bool is_v, int i) -> bool {
         const int b = is_v ? 2 : (i & 1), use = is_v ? i : (i >> 1);
-        if (use > 0 && !mbar_wait(&empty[b], (use - 1) & 1, abort)) return false;
-        mbar_expect_tx(&full[b], KV_BYTES);
+        if (use > 0 && !__all_sync(0xffffffffu, mbar_wait(&empty[b], (use - 1) & 1, abort))) return false;
+        if (elected) mbar_expect_tx(&full[b], KV_BYTES);
         const bool withheld = is_v && i == *(volatile int*)&tc_withhold_step;   // tests only
         for (int half = 0; half < (withheld ? 1 : 2); ++half) {
           const int page = pages[min(page_lo + 2 * i + half, page_hi)];
           const int row = (page * kv_heads + kvh) * SB_PAGE_TOKENS;
           for (int c = 0; c < DC; ++c)
-            tma_load_2d(ring + b * KV_BYTES + c * SUB + half * 8192, is_v ? &map_v : &map_k, &full[b], c * 64, row);
+            if (elected) tma_load_2d(ring + b * KV_BYTES + c * SUB + half * 8192, is_v ? &map_v : &map_k, &full[b], c * 64, row);
         }
         return true;
       };
@@ -298,7 +309,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (i + 1 < n_steps) { ok = load(false, i + 1); if (ok) loads[(i + 1) & 1]++; }
         if (ok) { ok = load(true, i); if (ok) loads[2]++; }
       }
-      if (*abort) {                                    // let the copies in flight land before the block ends
+      if (*abort && elected) {                         // let the copies in flight land before the block ends
         for (int b = 0; b < 3; ++b) {
           const uint64_t start = now_ns();
           while (loads[b] > 0 && !mbar_try(&full[b], (loads[b] - 1) & 1) && now_ns() - start < WAIT_LIMIT_NS) {}
@@ -309,37 +320,51 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     // ---------------- MMA issuers: warp 9 for tile 0, warp 10 for tile 1.  Each runs its own chain
     // of waits, so that one tile's waiting does not hold up the other's products.
     const int t = warp - 9, n_mine = n_tile[t], n_other = n_tile[1 - t];
-    if (lane == 0 && n_mine > 0) {
+    if (n_mine > 0) {
+      // the whole warp waits and computes descriptors; one elected lane issues (see the producer)
+      const bool elected = elect_one();
       const uint32_t idesc_s = instr_desc(TC_BK, 0), idesc_o = instr_desc(D, 1);
       const uint32_t q_addr = smem_u32(q_sm + t * Q_BYTES), p_addr = smem_u32(p_sm + t * P_BYTES);
       // S = Q K^T: k runs over the head in steps of 16 (32 bytes inside a 128-byte chunk)
       auto issue_s = [&](int buf) {
+        if (elected) {
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off = (k >> 2) * SUB + (k & 3) * 32;
-          umma_bf16(tmem_base + t * TC_BK, smem_desc(q_addr + off, 16),
-                    smem_desc(smem_u32(ring + buf * KV_BYTES) + off, 16), idesc_s, k > 0 ? 1u : 0u);
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t off = (k >> 2) * SUB + (k & 3) * 32;
+            umma_bf16(tmem_base + t * TC_BK, smem_desc(q_addr + off, 16),
+                      smem_desc(smem_u32(ring + buf * KV_BYTES) + off, 16), idesc_s, k > 0 ? 1u : 0u);
+          }
+          umma_commit(&s_ready[t]);
         }
-        umma_commit(&s_ready[t]);
       };
       // O (+)= P V: k runs over the 128 keys in steps of 16; P K-major (two 64-key chunks); V's
       // rows are keys (16 keys = 2048 bytes), its 64-wide chunks of the head are SUB bytes apart
       auto issue_pv = [&](bool first) {
+        if (elected) {
 #pragma unroll
-        for (int k = 0; k < TC_BK / 16; ++k) {
-          const uint32_t a_off = (k >> 2) * SUB + (k & 3) * 32;
-          umma_bf16(tmem_base + 2 * TC_BK + t * 128, smem_desc(p_addr + a_off, 16),
-                    smem_desc(smem_u32(ring + 2 * KV_BYTES) + k * 2048, SUB), idesc_o,
-                    (first && k == 0) ? 0u : 1u);
+          for (int k = 0; k < TC_BK / 16; ++k) {
+            const uint32_t a_off = (k >> 2) * SUB + (k & 3) * 32;
+            umma_bf16(tmem_base + 2 * TC_BK + t * 128, smem_desc(p_addr + a_off, 16),
+                      smem_desc(smem_u32(ring + 2 * KV_BYTES) + k * 2048, SUB), idesc_o,
+                      (first && k == 0) ? 0u : 1u);
+          }
+          umma_commit(&o_ready[t]);
         }
-        umma_commit(&o_ready[t]);
       };
       // A buffer is free after two arrivals, one per tile; a tile that is alone in a step makes both.
       auto release = [&](int buf, bool alone) {
-        umma_commit(&empty[buf]);
-        if (alone) umma_commit(&empty[buf]);
+        if (elected) {
+          umma_commit(&empty[buf]);
+          if (alone) umma_commit(&empty[buf]);
+        }
+        __syncwarp();
       };
-      bool ok = mbar_wait(&q_full, 0, abort) && mbar_wait(&full[0], 0, abort);
+      // every lane waits; the warp goes on together or stops together
+      auto wait2 = [&](uint64_t* first_bar, uint32_t first_parity, uint64_t* second_bar, uint32_t second_parity) -> bool {
+        const bool got = mbar_wait(first_bar, first_parity, abort) && mbar_wait(second_bar, second_parity, abort);
+        return __all_sync(0xffffffffu, got);
+      };
+      bool ok = wait2(&q_full, 0, &full[0], 0);
       if (ok) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         issue_s(0);
@@ -350,13 +375,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       for (int i = 0; i < n_mine && ok; ++i) {
         if (i + 1 < n_mine) {
           const int kb = (i + 1) & 1;                  // buffer of K(i+1); V(i) is in buffer 2
-          ok = mbar_wait(&full[kb], ((i + 1) >> 1) & 1, abort) && mbar_wait(&s_free[t], i & 1, abort);
+          ok = wait2(&full[kb], ((i + 1) >> 1) & 1, &s_free[t], i & 1);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           issue_s(kb);
           release(kb, i + 1 >= n_other);
         }
-        ok = mbar_wait(&full[2], i & 1, abort) && mbar_wait(&p_ready[t], i & 1, abort);
+        ok = wait2(&full[2], i & 1, &p_ready[t], i & 1);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         issue_pv(i == 0);

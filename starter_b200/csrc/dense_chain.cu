@@ -189,7 +189,8 @@ dense_chain_kernel(const __grid_constant__ DcMaps maps, const __grid_constant__ 
   float* norm_buf = reinterpret_cast<float*>(ring + (size_t)p.slots * SLOT_BYTES);
   __shared__ DcShared sh;
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // the warp's number as a value the compiler knows to be the same in every lane
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
   const int cta = blockIdx.x, n_ctas = gridDim.x;
   const int SLOTS = p.slots;
   const uint64_t limit = p.limit_ns;
@@ -211,8 +212,12 @@ dense_chain_kernel(const __grid_constant__ DcMaps maps, const __grid_constant__ 
   const uint32_t tmem = sh.tmem;
 
   if (warp == 0) {
-    // ---------------- weight producer: runs ahead of everything, bounded by the ring alone
-    if (lane == 0) {
+    // ---------------- weight producer: runs ahead of everything, bounded by the ring alone.  The
+    // whole warp walks the schedule and one elected lane issues the copies: addresses and coordinates
+    // are then the same in every lane and can live in the uniform registers the copies want (run by
+    // one lane inside a branch on the lane number, each copy or MMA costs over a hundred cycles to issue)
+    {
+      const bool elected = elect_one();
       int i = 0, lin = 0;
       for (int s = 0; s < p.n_stages && !*abort; ++s) {
         const DcStage& st = p.st[s];
@@ -220,32 +225,35 @@ dense_chain_kernel(const __grid_constant__ DcMaps maps, const __grid_constant__ 
         DcCut cut; cut.init(st, n_ctas);
         DcSegments seg; seg.init(cut, cta);
         int tile, k0, k1;
-        if (p.trace) p.trace[(size_t)cta * 64 + 32 + 2 * lin] = now_ns();
+        if (p.trace && elected) p.trace[(size_t)cta * 64 + 32 + 2 * lin] = now_ns();
         while (seg.next(tile, k0, k1)) {
           const int row_a = st.gated ? tile * 64 : tile * DC_TILE_N;
           const int row_b = st.gated ? st.n_out + tile * 64 : tile * DC_TILE_N + 64;
           for (int kb = k0; kb < k1; ++kb, ++i) {
             const int slot = i % SLOTS;
-            if (i >= SLOTS && !mbar_wait(&sh.empty[slot], ((i / SLOTS) - 1) & 1, abort, limit)) break;
+            if (i >= SLOTS && !__all_sync(0xffffffffu, mbar_wait(&sh.empty[slot], ((i / SLOTS) - 1) & 1, abort, limit))) break;
             uint8_t* dst = ring + (size_t)slot * SLOT_BYTES;
-            mbar_expect_tx(&sh.full[slot], DC_W_BYTES);
-            tma_load_2d(dst, &maps.w[lin], &sh.full[slot], kb * DC_TILE_K, row_a);
-            tma_load_2d(dst + DC_HALF_BYTES, &maps.w[lin], &sh.full[slot], kb * DC_TILE_K, row_b);
+            if (elected) {
+              mbar_expect_tx(&sh.full[slot], DC_W_BYTES);
+              tma_load_2d(dst, &maps.w[lin], &sh.full[slot], kb * DC_TILE_K, row_a);
+              tma_load_2d(dst + DC_HALF_BYTES, &maps.w[lin], &sh.full[slot], kb * DC_TILE_K, row_b);
+            }
           }
           if (*abort) break;
         }
-        if (p.trace) p.trace[(size_t)cta * 64 + 32 + 2 * lin + 1] = now_ns();
+        if (p.trace && elected) p.trace[(size_t)cta * 64 + 32 + 2 * lin + 1] = now_ns();
         ++lin;
       }
     }
   } else if (warp == 1) {
     // ---------------- activation producer: a stage's input exists once the stage before is complete
-    if (lane == 0) {
+    {
+      const bool elected = elect_one();
       int i = 0, lin = 0;
       for (int s = 0; s < p.n_stages && !*abort; ++s) {
         const DcStage& st = p.st[s];
         if (st.kind != DC_KIND_LINEAR) continue;
-        if (!mbar_wait(&sh.ready, lin & 1, abort, limit)) break;
+        if (!__all_sync(0xffffffffu, mbar_wait(&sh.ready, lin & 1, abort, limit))) break;
         if (lin == 0) pdl_wait();
         fence_async_global();
         DcCut cut; cut.init(st, n_ctas);
@@ -254,10 +262,12 @@ dense_chain_kernel(const __grid_constant__ DcMaps maps, const __grid_constant__ 
         while (seg.next(tile, k0, k1)) {
           for (int kb = k0; kb < k1; ++kb, ++i) {
             const int slot = i % SLOTS;
-            if (i >= SLOTS && !mbar_wait(&sh.empty[slot], ((i / SLOTS) - 1) & 1, abort, limit)) break;
-            mbar_expect_tx(&sh.full[slot], X_BYTES);
-            tma_load_2d(ring + (size_t)slot * SLOT_BYTES + DC_W_BYTES, &maps.x[lin], &sh.full[slot],
-                        kb * DC_TILE_K, 0);
+            if (i >= SLOTS && !__all_sync(0xffffffffu, mbar_wait(&sh.empty[slot], ((i / SLOTS) - 1) & 1, abort, limit))) break;
+            if (elected) {
+              mbar_expect_tx(&sh.full[slot], X_BYTES);
+              tma_load_2d(ring + (size_t)slot * SLOT_BYTES + DC_W_BYTES, &maps.x[lin], &sh.full[slot],
+                          kb * DC_TILE_K, 0);
+            }
           }
           if (*abort) break;
         }
@@ -266,7 +276,8 @@ dense_chain_kernel(const __grid_constant__ DcMaps maps, const __grid_constant__ 
     }
   } else if (warp == 2) {
     // ---------------- MMA issuer: one accumulator per range, two accumulators in turn
-    if (lane == 0) {
+    {
+      const bool elected = elect_one();
       const uint32_t idesc = instr_desc(BM);
       int i = 0, use = 0, lin = 0;
       for (int s = 0; s < p.n_stages && !*abort; ++s) {
@@ -277,28 +288,38 @@ dense_chain_kernel(const __grid_constant__ DcMaps maps, const __grid_constant__ 
         int tile, k0, k1;
         while (seg.next(tile, k0, k1)) {
           const int a = use & 1;
-          if (p.trace && p.trace[(size_t)cta * 64 + 48 + 2 * lin] == 0) {
-            mbar_wait(&sh.full[i % SLOTS], (i / SLOTS) & 1, abort, limit);
-            p.trace[(size_t)cta * 64 + 48 + 2 * lin] = now_ns();
+          if (p.trace) {
+            const bool first = elected && p.trace[(size_t)cta * 64 + 48 + 2 * lin] == 0;
+            if (__any_sync(0xffffffffu, first)) {
+              mbar_wait(&sh.full[i % SLOTS], (i / SLOTS) & 1, abort, limit);
+              if (first) p.trace[(size_t)cta * 64 + 48 + 2 * lin] = now_ns();
+            }
+            __syncwarp();
           }
-          if (use >= 2 && !mbar_wait(&sh.acc_empty[a], ((use >> 1) - 1) & 1, abort, limit)) break;
+          if (use >= 2 && !__all_sync(0xffffffffu, mbar_wait(&sh.acc_empty[a], ((use >> 1) - 1) & 1, abort, limit))) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t acc = tmem + (uint32_t)(a * BM);
           for (int kb = k0; kb < k1; ++kb, ++i) {
             const int slot = i % SLOTS;
-            if (!mbar_wait(&sh.full[slot], (i / SLOTS) & 1, abort, limit)) break;
+            if (!__all_sync(0xffffffffu, mbar_wait(&sh.full[slot], (i / SLOTS) & 1, abort, limit))) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t a_addr = smem_u32(ring + (size_t)slot * SLOT_BYTES);
             const uint64_t a_desc = smem_desc(a_addr), b_desc = smem_desc(a_addr + DC_W_BYTES);
+            if (elected) {
 #pragma unroll
-            for (int k = 0; k < DC_TILE_K / 16; ++k)
-              umma_bf16(acc, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > k0 || k > 0) ? 1u : 0u);
-            umma_commit(&sh.empty[slot]);
+              for (int k = 0; k < DC_TILE_K / 16; ++k)
+                umma_bf16(acc, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > k0 || k > 0) ? 1u : 0u);
+              umma_commit(&sh.empty[slot]);
+            }
+            __syncwarp();
           }
-          if (*abort) break;
-          umma_commit(&sh.acc_full[a]);
+          if (__any_sync(0xffffffffu, *abort != 0)) break;
+          if (elected) {
+            umma_commit(&sh.acc_full[a]);
+            if (p.trace) p.trace[(size_t)cta * 64 + 48 + 2 * lin + 1] = now_ns();
+          }
+          __syncwarp();
           ++use;
-          if (p.trace) p.trace[(size_t)cta * 64 + 48 + 2 * lin + 1] = now_ns();
         }
         ++lin;
       }

@@ -1,8 +1,8 @@
 """Python face of the CUDA kernels: argument checks, output allocation, launch on the current stream.
 
 Every function here runs a hand-written kernel from ``starter_b200/csrc`` (the one
-exception, the prompt-sized bfloat16 matrix product, goes to the vendor's GEMM
-library exactly where the reference does, engine/engine.py:431-450).  There is no
+exception: a bfloat16 matrix product of 65 to 511 rows goes to the vendor's GEMM
+library, where the reference uses one too, engine/engine.py:431-450).  There is no
 CPU path: tensors must live on a CUDA device, and a shape a kernel cannot take is
 refused with an error that names it.
 """
@@ -17,12 +17,18 @@ from .cache.layout import PAGE_TOKENS
 from .csrc import build
 
 SMALL_ROWS = 16
-#: Up to this many rows the bfloat16 product runs on this library's tcgen05 kernel, where it is bound
-#: by streaming the weights; beyond it (prompts, longer chunks) the vendor's GEMM is used, as the
-#: reference does (engine/engine.py:431-450).  Measured on the four projections of a 2560-wide layer:
-#: 63-70 us a layer for the own kernel up to 64 rows against 64-86 for the library; 78 against 78 at
-#: 96 rows, 79 against 69 at 128 and 103 against 73 at 256 with the best plan found for each.
+#: Up to this many rows the bfloat16 product runs on this library's few-row tcgen05 kernel
+#: (csrc/gemm_tcgen05.cu), where it is bound by streaming the weights.  Measured on the four
+#: projections of a 2560-wide layer: 63-70 us a layer up to 64 rows against 64-86 for the vendor's
+#: library; 78 against 78 at 96 rows, 79 against 69 at 128 and 103 against 73 at 256.
 TENSOR_CORE_MAX_ROWS = 64
+#: From this many rows on it runs on this library's persistent CTA-pair kernel
+#: (csrc/gemm_prompt_tcgen05.cu), whose tiles are 256 rows high.  Measured a layer against the
+#: vendor's library (which needs a separate SwiGLU kernel): 114 against 106 us at 512 rows, 167
+#: against 164 at 1,024, 298 against 307 at 2,048, 434 against 470 at 3,072; at 256 rows 100 against
+#: 75.  In between (65 to 511 rows) the vendor's GEMM is used, as the reference does from 33 rows on
+#: (engine/engine.py:431-450).
+PROMPT_MIN_ROWS = 512
 MAX_HEAD_DIM = 256
 
 _DT = {torch.float32: 0, torch.bfloat16: 1}
@@ -212,6 +218,8 @@ def linear(x, weight, out_float=False, gated=False, status=None):
         _check(rc, "sgemm")
     elif out_float:
         y = torch.mm(x, weight.t(), out_dtype=torch.float32)
+    elif rows >= PROMPT_MIN_ROWS and k_dim % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0:
+        return linear_prompt(x, weight, gated=gated, status=status)
     else:
         y = torch.mm(x, weight.t())
     return swiglu(y) if gated else y

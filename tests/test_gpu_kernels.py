@@ -422,6 +422,93 @@ def test_a_wait_in_the_tensor_core_product_that_runs_out_is_reported(rows, n, k,
     assert torch.allclose(got.cpu().double(), ref, atol=2e-2, rtol=2e-2) and status.item() == 0
 
 
+@pytest.mark.parametrize("rows,n,k,gated,bn,pairs", [
+    (256, 256, 128, False, 256, 1), (512, 512, 192, False, 0, 0), (300, 200, 72, False, 0, 0),
+    (300, 320, 136, False, 160, 0), (1, 64, 8, False, 64, 0), (700, 777, 264, False, 192, 3),
+    (256, 128, 128, True, 256, 1), (700, 448, 264, True, 0, 0), (333, 192, 200, True, 128, 0),
+    (65, 100, 40, True, 64, 0), (2048, 2560, 1024, False, 0, 0), (1100, 1216, 2560, True, 0, 0)])
+def test_prompt_product(rows, n, k, gated, bn, pairs):
+    """The CTA-pair product for many rows at sizes that are no multiples of its tiles (rows past the
+    end of a 256-row tile, widths past the end of a weight tile, a k that ends inside a 64-wide
+    block), every tile width, one pair or all of them (so that a pair works through several tiles
+    and both accumulators), plain and gated; twice, and bit-equal both times."""
+    from starter_b200 import ops
+
+    x = rand(rows, k, dtype="bfloat16", seed=52)
+    w = rand(n * (2 if gated else 1), k, dtype="bfloat16", seed=53, scale=0.05)
+    ref = x.double() @ w.double().t()
+    if gated:
+        gu = ref.to(torch.bfloat16)
+        ref = plain.plain_swiglu(gu[:, :n], gu[:, n:]).double()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    got = ops.linear_prompt(dev(x), dev(w), gated=gated, bn=bn, pairs=pairs, status=status)
+    assert got.shape == (rows, n) and got.dtype == torch.bfloat16
+    assert torch.allclose(got.cpu().double(), ref, atol=2e-2, rtol=2e-2)
+    again = ops.linear_prompt(dev(x), dev(w), gated=gated, bn=bn, pairs=pairs, status=status)
+    assert torch.equal(got, again)
+    assert status.item() == 0
+
+
+def test_prompt_product_is_the_few_row_product_row_by_row():
+    """A prompt's rows through the CTA-pair kernel and the same rows, 16 at a time, through the
+    kernel that decoding uses: the same sums in another order, so equal to rounding (and the gated
+    epilogue rounds at the same places)."""
+    from starter_b200 import ops
+
+    x = dev(rand(600, 520, dtype="bfloat16", seed=54))
+    for gated in (False, True):
+        w = dev(rand(384 * (2 if gated else 1), 520, dtype="bfloat16", seed=55, scale=0.05))
+        many = ops.linear_prompt(x, w, gated=gated)
+        few = torch.cat([ops.linear_tensor_core(x[i:i + 16].contiguous(), w, gated=gated) for i in range(0, 600, 16)])
+        assert torch.allclose(many.float(), few.float(), atol=2e-2, rtol=2e-2)
+        assert (many != few).float().mean().item() < 0.05
+
+
+def test_linear_sends_each_row_count_to_its_kernel(monkeypatch):
+    """``ops.linear`` in bfloat16: the tcgen05 product up to TENSOR_CORE_MAX_ROWS rows, the CTA-pair
+    product from PROMPT_MIN_ROWS rows on, and both agree with the plain product."""
+    from starter_b200 import ops
+
+    taken = []
+    few, many = ops.linear_tensor_core, ops.linear_prompt
+    monkeypatch.setattr(ops, "linear_tensor_core", lambda *a, **k: (taken.append("few"), few(*a, **k))[1])
+    monkeypatch.setattr(ops, "linear_prompt", lambda *a, **k: (taken.append("many"), many(*a, **k))[1])
+    w = rand(200, 264, dtype="bfloat16", seed=57, scale=0.05)
+    for rows, want in ((ops.TENSOR_CORE_MAX_ROWS, "few"), (ops.PROMPT_MIN_ROWS, "many"), (ops.PROMPT_MIN_ROWS + 77, "many")):
+        x = rand(rows, 264, dtype="bfloat16", seed=56)
+        got = ops.linear(dev(x), dev(w))
+        assert taken[-1] == want
+        assert torch.allclose(got.cpu().double(), x.double() @ w.double().t(), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("rows,n,k,gated,kblock", [(256, 256, 512, False, 0), (600, 384, 1024, True, 3)])
+def test_a_wait_in_the_prompt_product_that_runs_out_is_reported(rows, n, k, gated, kblock):
+    """One weight copy of every first CTA is left out on purpose (an entry point made for this): the
+    stage never fills, the waits of both CTAs of the pair give up after 2 ms, the kernel returns with
+    its tensor memory freed, the status word says so; the same product, run normally afterwards, is
+    right."""
+    from starter_b200 import ops
+    from starter_b200.engine.runner import ModelRunner
+
+    x = rand(rows, k, dtype="bfloat16", seed=62)
+    w = rand(n * (2 if gated else 1), k, dtype="bfloat16", seed=63, scale=0.05)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.linear_prompt(dev(x), dev(w), gated=gated, status=status, withhold=(kblock, 2_000_000))
+    torch.cuda.synchronize()
+    assert status.item() == 4
+    holder = ModelRunner.__new__(ModelRunner)
+    holder.status = status
+    with pytest.raises(RuntimeError, match="tensor-core product ran out of time"):
+        holder.check_status()
+    assert status.item() == 0
+    got = ops.linear_prompt(dev(x), dev(w), gated=gated, status=status)
+    ref = x.double() @ w.double().t()
+    if gated:
+        gu = ref.to(torch.bfloat16)
+        ref = plain.plain_swiglu(gu[:, :n], gu[:, n:]).double()
+    assert torch.allclose(got.cpu().double(), ref, atol=2e-2, rtol=2e-2) and status.item() == 0
+
+
 @pytest.mark.parametrize("heads,kv_heads,d,window", [(4, 2, 16, None), (6, 2, 32, 5), (8, 8, 128, None),
                                                     (8, 1, 64, 70), (32, 8, 128, None), (4, 4, 64, 64),
                                                     (6, 3, 128, 130)])
