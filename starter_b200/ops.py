@@ -249,16 +249,19 @@ def gemm_plan(rows: int, n_out: int, k_dim: int, gated: bool):
     k_blocks = -(-k_dim // 64)
     stage_bytes = 16384 + bm * 128
     if rows <= 64:
-        # measured: rings deeper than four stages lose (fewer CTAs fit on an SM); the product is
-        # fastest with about 70% of the CTA slots taken and all CTAs resident at once; when three
+        if tiles * 6 <= 148 and k_blocks >= 24:
+            # few tiles (a narrow output): no more CTAs than SMs, each with the deepest ring
+            return bm, min(6, 148 // tiles), 8
+        # otherwise: rings deeper than four stages lose (fewer CTAs fit on an SM); the product is
+        # fastest with about 80% of the CTA slots taken and all CTAs resident at once; when three
         # stages let a third CTA onto each SM and that buys clearly more CTAs, three stages win
         def choice(stages):
             slots = 148 * ((227 * 1024) // (stages * stage_bytes + 2048))
-            return slots, max(1, min(8, k_blocks // 4, int(0.7 * slots) // tiles))
+            return slots, max(1, min(8, k_blocks // 4, int(0.82 * slots) // tiles))
 
         slots4, splits4 = choice(4)
         slots3, splits3 = choice(3)
-        if bm > 16 and slots3 > slots4 and (tiles > slots4 or tiles * splits3 > 1.3 * tiles * splits4):
+        if bm > 16 and slots3 > slots4 and (tiles > slots4 or tiles * splits3 > 1.5 * tiles * splits4):
             stages, splits = 3, splits3
         else:
             stages, splits = 4, splits4
