@@ -104,6 +104,7 @@ __device__ __forceinline__ uint32_t pg_instr_desc(int bn) {
 
 struct PromptGemmArgs {
   bf16* out;            // [rows, n_out]
+  const bf16* residual; // [rows, n_out] or null: out = round(residual + round(product)); may be `out` itself
   int* status;
   int rows, n_out, k_dim;
   int bn;               // weight rows per tile (the MMA's N); with gated, bn / 2 gate and bn / 2 up rows
@@ -115,11 +116,31 @@ struct PromptGemmArgs {
 
 // ------------------------------------------------------------------------------------------ kernel
 
-// 32 values of row `grow` starting at column `col` of out, rounded to bfloat16.
-__device__ __forceinline__ void pg_store32(const PromptGemmArgs& args, int grow, int col, const float* v) {
+// 32 values of row `grow` starting at column `col` of out, rounded to bfloat16; with a residual
+// stream, the rounded product is added to the stream's values first (the sum in float, rounded once
+// more: what a separate add of two bfloat16 tensors gives, engine/engine.py:734-736).
+__device__ __forceinline__ void pg_store32(const PromptGemmArgs& args, int grow, int col, float* v) {
   if (grow >= args.rows || col >= args.n_out) return;
-  bf16* at = args.out + (size_t)grow * args.n_out + col;
-  if (args.n_out % 8 == 0 && col + 32 <= args.n_out) {
+  const size_t offset = (size_t)grow * args.n_out + col;
+  bf16* at = args.out + offset;
+  const bool wide = args.n_out % 8 == 0 && col + 32 <= args.n_out;
+  if (args.residual) {
+    const bf16* res = args.residual + offset;
+    if (wide) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(res + j);
+        const bf16* e = reinterpret_cast<const bf16*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[j + i] = __bfloat162float(e[i]) + rnd<bf16>(v[j + i]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col + j < args.n_out) v[j] = __bfloat162float(res[j]) + rnd<bf16>(v[j]);
+    }
+  }
+  if (wide) {
 #pragma unroll
     for (int j = 0; j < 32; j += 8) {
       __nv_bfloat162 p0 = __floats2bfloat162_rn(v[j], v[j + 1]), p1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
@@ -366,10 +387,10 @@ static int pg_launch(const CUtensorMap& map_x, const CUtensorMap& map_w, const P
 }
 
 // x [rows, k_dim] and w [n_out (2 * n_out if gated), k_dim] bfloat16, row-major, 16-byte aligned, k_dim
-// a multiple of 8; out [rows, n_out] bfloat16.  bn (0: chosen here) is the number of weight rows per
+// a multiple of 8; out [rows, n_out] bfloat16; residual null or [rows, n_out] bfloat16 (not with gated).  bn (0: chosen here) is the number of weight rows per
 // tile: a multiple of 32 from 64 to 256 (of 64 if gated); pairs (0: one per two SMs) the number of CTA
 // pairs.  Returns -2 for sizes it does not take, -3/-4 if the tensor maps cannot be made.
-static int pg_entry(const void* x, const void* w, void* out, int rows, int n_out, int k_dim, int bn, int pairs,
+static int pg_entry(const void* x, const void* w, void* out, const void* residual, int rows, int n_out, int k_dim, int bn, int pairs,
                     int gated, int* status, unsigned long long wait_limit_ns, int withhold_kblock,
                     cudaStream_t s) {
   if (rows == 0 || n_out == 0) return 0;
@@ -408,7 +429,8 @@ static int pg_entry(const void* x, const void* w, void* out, int rows, int n_out
   rc = pg_make_map(&map_w, w, gated ? 2ll * n_out : n_out, k_dim, bn / 2);
   if (rc) return rc;
   PromptGemmArgs args;
-  args.out = (bf16*)out; args.status = status;
+  if (residual && gated) return -2;
+  args.out = (bf16*)out; args.residual = (const bf16*)residual; args.status = status;
   args.rows = rows; args.n_out = n_out; args.k_dim = k_dim;
   args.bn = bn; args.stages = stages; args.gated = gated;
   args.m_tiles = m_tiles; args.n_tiles = n_tiles;
@@ -420,9 +442,9 @@ static int pg_entry(const void* x, const void* w, void* out, int rows, int n_out
 
 extern "C" {
 
-int sb_gemm_prompt(const void* x, const void* w, void* out, int rows, int n_out, int k_dim, int bn, int pairs,
+int sb_gemm_prompt(const void* x, const void* w, void* out, const void* residual, int rows, int n_out, int k_dim, int bn, int pairs,
                    int gated, int* status, cudaStream_t s) {
-  return pg_entry(x, w, out, rows, n_out, k_dim, bn, pairs, gated, status, TC_WAIT_LIMIT_NS, -1, s);
+  return pg_entry(x, w, out, residual, rows, n_out, k_dim, bn, pairs, gated, status, TC_WAIT_LIMIT_NS, -1, s);
 }
 
 // The same product with one weight copy left out on purpose (k-block `withhold_kblock` of the first
@@ -432,7 +454,7 @@ int sb_gemm_prompt_withheld(const void* x, const void* w, void* out, int rows, i
                             int pairs, int gated, int* status, unsigned long long wait_limit_ns,
                             int withhold_kblock, cudaStream_t s) {
   if (withhold_kblock < 0 || wait_limit_ns == 0) return -2;
-  return pg_entry(x, w, out, rows, n_out, k_dim, bn, pairs, gated, status, wait_limit_ns, withhold_kblock, s);
+  return pg_entry(x, w, out, nullptr, rows, n_out, k_dim, bn, pairs, gated, status, wait_limit_ns, withhold_kblock, s);
 }
 
 }  // extern "C"

@@ -94,6 +94,16 @@ def _need(t, name, dtype=None, ndim=None):
     raise KernelError(f"{name} must have {ndim} dimensions, got shape {tuple(t.shape)}")
 
 
+class _Added:
+    """What ``linear`` returns when it has put its result onto ``add_to`` instead of returning it."""
+
+    def __repr__(self):
+        return "ADDED"
+
+
+#: the value that stands for "already added onto the residual stream" (see ``linear``'s ``add_to``)
+ADDED = _Added()
+
 #: how many kernels of this library have been launched by this process (library GEMMs not counted)
 launch_count = 0
 #: switch for the decode attention's reads before its dependent-launch wait (see attention_decode_qkv)
@@ -181,8 +191,13 @@ def swiglu(gate_up):
 
 # ---------------------------------------------------------------------------------------- matrix products
 
-def linear(x, weight, out_float=False, gated=False, status=None):
+def linear(x, weight, out_float=False, gated=False, status=None, add_to=None):
     """``x @ weight.T`` for ``x`` ``[T, K]`` and ``weight`` ``[N, K]`` (no bias).
+
+    ``add_to`` (``[T, N]``, the residual stream) is an offer, not an order: where the kernel that
+    runs has an epilogue for it (the prompt product), ``add_to`` becomes
+    ``round(add_to + round(product))`` in place and ``ADDED`` is returned; otherwise ``add_to`` is
+    left alone and the product is returned as usual.
 
     ``gated``: ``weight`` is ``[gate; up]`` stacked (``[2 * I, K]``) and the result is
     ``round(silu(x @ gate.T)) * (x @ up.T)`` of shape ``[T, I]``.  ``out_float``
@@ -219,6 +234,10 @@ def linear(x, weight, out_float=False, gated=False, status=None):
     elif out_float:
         y = torch.mm(x, weight.t(), out_dtype=torch.float32)
     elif rows >= PROMPT_MIN_ROWS and k_dim % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0:
+        if (add_to is not None and not gated and add_to.dtype == torch.bfloat16 and add_to.is_contiguous()
+                and tuple(add_to.shape) == (rows, n_out)):
+            linear_prompt(x, weight, status=status, residual=add_to)
+            return ADDED
         return linear_prompt(x, weight, gated=gated, status=status)
     else:
         y = torch.mm(x, weight.t())
@@ -314,13 +333,15 @@ def linear_tensor_core(x, weight, out_float=False, gated=False, bm=None, splits=
     return out
 
 
-def linear_prompt(x, weight, gated=False, bn=0, pairs=0, status=None, withhold=None):
+def linear_prompt(x, weight, gated=False, bn=0, pairs=0, status=None, withhold=None, residual=None):
     """The bfloat16 product for many rows: the persistent CTA-pair kernel (csrc/gemm_prompt_tcgen05.cu).
 
     ``bn`` is the number of weight rows per tile (0: chosen by the kernel's host side), ``pairs`` the
     number of CTA pairs (0: one per two SMs).  ``withhold = (k_block, limit_ns)`` is for tests of the
     give-up path: one weight copy is left out, a wait runs out after ``limit_ns``, the kernel returns,
-    bit 4 of ``status`` is set and the result is undefined."""
+    bit 4 of ``status`` is set and the result is undefined.  With ``residual`` (``[rows, n]``
+    bfloat16, not with ``gated``) the result is ``round(residual + round(product))``, written into
+    ``residual`` itself, which is returned."""
     _need(x, "x", torch.bfloat16, 2)
     _need(weight, "weight", torch.bfloat16, 2)
     rows, k_dim = x.shape
@@ -330,14 +351,21 @@ def linear_prompt(x, weight, gated=False, bn=0, pairs=0, status=None, withhold=N
         raise KernelError(f"weight {tuple(weight.shape)} does not take inputs of width {k_dim}")
     if k_dim % 8 or (gated and n_total % 2) or x.data_ptr() % 16 or weight.data_ptr() % 16:
         raise KernelError(f"the prompt product needs k % 8 == 0 and 16-byte aligned operands; got k = {k_dim}")
-    out = torch.empty((rows, n_out), dtype=torch.bfloat16, device=x.device)
+    if residual is not None:
+        _need(residual, "residual", torch.bfloat16, 2)
+        if gated or tuple(residual.shape) != (rows, n_out) or withhold is not None:
+            raise KernelError(f"a residual of shape {tuple(residual.shape)} cannot take a "
+                              f"{'gated ' if gated else ''}product of shape {(rows, n_out)}")
+        out = residual
+    else:
+        out = torch.empty((rows, n_out), dtype=torch.bfloat16, device=x.device)
     lib = _lib("gemm_prompt_tcgen05")
     if withhold is not None:
         rc = lib.sb_gemm_prompt_withheld(_ptr(x), _ptr(weight), _ptr(out), rows, n_out, k_dim, int(bn), int(pairs),
                                          int(gated), _ptr(status), ctypes.c_ulonglong(int(withhold[1])),
                                          int(withhold[0]), _stream())
     else:
-        rc = lib.sb_gemm_prompt(_ptr(x), _ptr(weight), _ptr(out), rows, n_out, k_dim, int(bn), int(pairs),
+        rc = lib.sb_gemm_prompt(_ptr(x), _ptr(weight), _ptr(out), _ptr(residual), rows, n_out, k_dim, int(bn), int(pairs),
                                 int(gated), _ptr(status), _stream())
     if rc in (-3, -4):
         raise KernelError("the TMA descriptors for the prompt product could not be made "

@@ -72,7 +72,9 @@ class GroupedQueryAttention(Part):
                              "this attention takes rotary positions (or none)")
         return rotation()
 
-    def __call__(self, x, ctx, entry, writes_cache=True):
+    adds_to_stream = True
+
+    def __call__(self, x, ctx, entry, writes_cache=True, add_to=None):
         s = self.spec
         cache = ctx.cache
         keys, values = cache.entry_pages(entry)
@@ -88,7 +90,7 @@ class GroupedQueryAttention(Part):
                                          write_cache=writes_cache, kv_hint=ctx.max_kv_len,
                                          # this layer alone writes the pages it reads in this step
                                          early=ctx.fenced and writes_cache)
-            return ops.linear(a, self.o, status=ctx.status)
+            return ops.linear(a, self.o, status=ctx.status, add_to=add_to)
         q = ops.qk_norm_rope_store(
             qkv, s.num_heads, s.num_kv_heads, s.head_dim, self.q_norm, self.k_norm, s.qk_norm_eps,
             cos, sin, ctx.tok_pos, ctx.tok_slot, cache.block_table, keys, values,
@@ -106,7 +108,7 @@ class GroupedQueryAttention(Part):
         else:
             a = ops.attention_rowwise(q, keys, values, cache.block_table, ctx.tok_slot, ctx.tok_pos,
                                       s.num_heads, s.num_kv_heads, s.head_dim, s.scale, s.window)
-        return ops.linear(a, self.o, status=ctx.status)
+        return ops.linear(a, self.o, status=ctx.status, add_to=add_to)
 
     def weight_bytes(self):
         return bytes_of(self.qkv, self.o, self.q_norm, self.k_norm)

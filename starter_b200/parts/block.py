@@ -7,6 +7,10 @@ is the previous block's output not yet added, and returns the same pair
 (engine/engine.py:669-673).  The model's final norm closes the chain the same way.
 A block does not know its neighbours or the model it is in.
 
+A mixer or feed-forward that sets ``adds_to_stream = True`` is called with ``add_to=residual``: it
+may add its output onto that tensor itself (in the epilogue of its last product) and return
+``ops.ADDED`` instead of the output; the norm that follows then only norms.
+
 An arrangement says which parts it is made of: ``FAMILIES`` maps each part's name inside the layer
 to the family its spec is looked up in.  The model builds exactly those parts from the layer spec
 and hands them over by name; ``mixer`` names the part that owns the layer's cache entry.
@@ -30,6 +34,11 @@ class PreNormBlock:
 
     def __call__(self, residual, pending, ctx, entry, writes_cache=True):
         n = self.norm1.add(residual, pending)
-        a = self.mixer(n, ctx, entry, writes_cache)
+        if getattr(self.mixer, "adds_to_stream", False):
+            a = self.mixer(n, ctx, entry, writes_cache, add_to=residual)
+        else:
+            a = self.mixer(n, ctx, entry, writes_cache)
         m = self.norm2.add(residual, a)
+        if getattr(self.feed_forward, "adds_to_stream", False):
+            return residual, self.feed_forward(m, ctx, add_to=residual)
         return residual, self.feed_forward(m, ctx)

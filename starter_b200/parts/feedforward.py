@@ -25,10 +25,12 @@ class GatedFeedForward(Part):
         self.gate_up = torch.cat([params["gate"], params["up"]], dim=0).contiguous()
         self.down = params["down"].contiguous()
 
-    def __call__(self, x, ctx=None):
+    adds_to_stream = True
+
+    def __call__(self, x, ctx=None, add_to=None):
         status = ctx.status if ctx is not None else None
         act = ops.linear(x, self.gate_up, gated=True, status=status)
-        return ops.linear(act, self.down, status=status)
+        return ops.linear(act, self.down, status=status, add_to=add_to)
 
     def weight_bytes(self):
         return bytes_of(self.gate_up, self.down)

@@ -21,12 +21,14 @@ class RMSNorm(Part):
 
     def add(self, residual, delta):
         """``residual += delta`` in place, then the norm of the sum (engine/kernels/fused.py:115-144)."""
-        if delta is None:
+        if delta is None or delta is ops.ADDED:      # nothing open, or the part before added it itself
             return ops.rmsnorm(residual, self.weight, self.spec.eps)
         return ops.rmsnorm(residual, self.weight, self.spec.eps, delta=delta)
 
     def add_rows(self, residual, delta, rows):
         """The norm of ``(residual + delta)[rows]`` without touching ``residual``."""
+        if delta is ops.ADDED:
+            delta = None
         return ops.rmsnorm(residual, self.weight, self.spec.eps, delta=delta, rows=rows)
 
     def weight_bytes(self):

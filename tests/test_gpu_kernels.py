@@ -449,6 +449,31 @@ def test_prompt_product(rows, n, k, gated, bn, pairs):
     assert status.item() == 0
 
 
+@pytest.mark.parametrize("rows,n,k,bn", [(512, 256, 128, 0), (700, 777, 264, 192), (300, 200, 72, 0), (2048, 2560, 512, 0)])
+def test_prompt_product_adds_onto_the_residual_stream(rows, n, k, bn):
+    """The residual epilogue: the stream becomes round(stream + round(product)) in place, exactly
+    what the product followed by a separate bfloat16 add gives; and ``ops.linear`` takes the offer
+    only where that kernel runs."""
+    from starter_b200 import ops
+
+    x = dev(rand(rows, k, dtype="bfloat16", seed=64))
+    w = dev(rand(n, k, dtype="bfloat16", seed=65, scale=0.05))
+    stream = dev(rand(rows, n, dtype="bfloat16", seed=66))
+    product = ops.linear_prompt(x, w, bn=bn)
+    want = (stream.float() + product.float()).to(torch.bfloat16)
+    got = stream.clone()
+    back = ops.linear_prompt(x, w, bn=bn, residual=got)
+    assert back is got and torch.equal(got, want)
+    offered = stream.clone()
+    answer = ops.linear(x, w, add_to=offered)
+    if rows >= ops.PROMPT_MIN_ROWS:
+        assert answer is ops.ADDED and torch.equal(offered, want)
+    else:
+        assert torch.equal(offered, stream) and torch.allclose(answer.float(), product.float(), atol=2e-2, rtol=2e-2)
+    with pytest.raises(ops.KernelError, match="residual"):
+        ops.linear_prompt(x, w, residual=stream[:, :-8].contiguous())
+
+
 def test_prompt_product_is_the_few_row_product_row_by_row():
     """A prompt's rows through the CTA-pair kernel and the same rows, 16 at a time, through the
     kernel that decoding uses: the same sums in another order, so equal to rounding (and the gated

@@ -255,3 +255,38 @@ def test_bfloat16_engine_against_the_plain_implementation_run_in_bfloat16(tmp_pa
     rows += [runner.step([StepEntry(slot, [t], [0])]) for t in seq[100:]]
     runner.close_sequence(slot)
     assert_close(torch.cat(rows), want, "bfloat16", f"{name} 100 + 50 x 1, against the plain bfloat16 run")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", CONFIGS)
+def test_prompts_long_enough_for_the_prompt_product(tmp_path_factory, name, dtype):
+    """Steps of 512 rows and more take other kernels in bfloat16 (the CTA-pair product with its gated
+    and residual epilogues, 256-query attention blocks): one long prompt whole, two long prompts of
+    unequal length packed into one step, and a long prompt followed by a short chunk and single
+    tokens, all against the plain implementation."""
+    from starter_b200 import ops
+    from starter_b200.engine import StepEntry
+
+    _, cfg, w = model_case(tmp_path_factory, name)
+    runner = runner_for(tmp_path_factory, name, dtype, max_tokens=64 * 48)
+    a = random_prompt(700, cfg["vocab_size"], 71)
+    b = random_prompt(ops.PROMPT_MIN_ROWS + 1, cfg["vocab_size"], 72)
+    want_a, want_b = plain.plain_forward(cfg, w, a), plain.plain_forward(cfg, w, b)
+    slot = runner.open_sequence()
+    got = runner.step([StepEntry(slot, a, all_places(len(a)))])
+    runner.close_sequence(slot)
+    assert_close(got, want_a, dtype, f"{name} one prompt of {len(a)}")
+    sa, sb = runner.open_sequence(), runner.open_sequence()
+    got = runner.step([StepEntry(sa, a, [0, 350, 699]), StepEntry(sb, b, all_places(len(b)))])
+    runner.close_sequence(sa)
+    runner.close_sequence(sb)
+    assert_close(got[:3], want_a[[0, 350, 699]], dtype, f"{name} the longer of two packed prompts")
+    assert_close(got[3:], want_b, dtype, f"{name} the shorter of two packed prompts")
+    slot = runner.open_sequence()
+    rows = [runner.step([StepEntry(slot, a[:600], all_places(600))]),
+            runner.step([StepEntry(slot, a[600:690], all_places(90))])]
+    rows += [runner.step([StepEntry(slot, [t], [0])]) for t in a[690:]]
+    runner.close_sequence(slot)
+    assert_close(torch.cat(rows), want_a, dtype, f"{name} 600 + 90 + 10 x 1")
+    runner.check_status()
+    runner.cache.check()
