@@ -1,7 +1,7 @@
 """Python face of the CUDA kernels: argument checks, output allocation, launch on the current stream.
 
 Every function here runs a hand-written kernel from ``starter_b200/csrc`` (the one
-exception: a bfloat16 matrix product of 65 to 511 rows goes to the vendor's GEMM
+exception: a bfloat16 matrix product of 129 to 511 rows goes to the vendor's GEMM
 library, where the reference uses one too, engine/engine.py:431-450).  There is no
 CPU path: tensors must live on a CUDA device, and a shape a kernel cannot take is
 refused with an error that names it.
@@ -20,13 +20,13 @@ SMALL_ROWS = 16
 #: Up to this many rows the bfloat16 product runs on this library's few-row tcgen05 kernel
 #: (csrc/gemm_tcgen05.cu), where it is bound by streaming the weights.  Measured on the four
 #: projections of a 2560-wide layer: 63-70 us a layer up to 64 rows against 64-86 for the vendor's
-#: library; 78 against 78 at 96 rows, 79 against 69 at 128 and 103 against 73 at 256.
-TENSOR_CORE_MAX_ROWS = 64
+#: library; 66 against 68-77 at 96 rows, 70 against 68 at 128, 95-102 against 73 at 192.
+TENSOR_CORE_MAX_ROWS = 128
 #: From this many rows on it runs on this library's persistent CTA-pair kernel
 #: (csrc/gemm_prompt_tcgen05.cu), whose tiles are 256 rows high.  Measured a layer against the
 #: vendor's library (which needs a separate SwiGLU kernel): 114 against 106 us at 512 rows, 167
 #: against 164 at 1,024, 298 against 307 at 2,048, 434 against 470 at 3,072; at 256 rows 100 against
-#: 75.  In between (65 to 511 rows) the vendor's GEMM is used, as the reference does from 33 rows on
+#: 75.  In between (129 to 511 rows) the vendor's GEMM is used, as the reference does from 33 rows on
 #: (engine/engine.py:431-450).
 PROMPT_MIN_ROWS = 512
 MAX_HEAD_DIM = 256
@@ -285,11 +285,15 @@ def gemm_plan(rows: int, n_out: int, k_dim: int, gated: bool):
         else:
             stages, splits = 4, splits4
     else:
-        # measured at 96 to 256 rows: 128-row tiles, two CTAs of three stages on an SM and up to four
-        # CTAs sharing a tile's k range; when there are more tiles than such CTAs fit at once, two
-        # stages (three CTAs on an SM) and two CTAs a tile
+        # measured at 96 to 500 rows (128-row tiles).  Few tiles: one CTA of six stages per SM and up
+        # to four CTAs sharing a tile's k range.  More tiles than SMs: two stages (three CTAs on an
+        # SM), and two CTAs a tile while there is one row tile.  In between: three stages.
         slots3 = 148 * ((227 * 1024) // (3 * stage_bytes + 2048))
-        if tiles > slots3:
+        if tiles <= 74:
+            # (clusters of three were measured far slower than of two or four here)
+            splits = max(1, min(4, k_blocks // 8, 148 // tiles))
+            stages, splits = 6, (2 if splits == 3 else splits)
+        elif tiles > 148:
             stages, splits = 2, (2 if rows <= 128 and k_blocks >= 16 else 1)
         else:
             stages, splits = 3, max(1, min(4, k_blocks // 8, slots3 // tiles))
@@ -317,6 +321,7 @@ def linear_tensor_core(x, weight, out_float=False, gated=False, bm=None, splits=
     bm = bm or plan[0]
     splits = splits or plan[1]
     stages = stages or max(plan[2], -(-bm * 512 // (16384 + bm * 128)))
+    stages = min(stages, (226 * 1024) // (16384 + bm * 128))     # a tile height other than the plan's
     out = torch.empty((rows, n_out), dtype=torch.float32 if out_float else torch.bfloat16, device=x.device)
     if withhold is not None:
         rc = _lib("gemm_tcgen05").sb_gemm_tcgen05_withheld(
