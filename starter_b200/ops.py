@@ -268,9 +268,20 @@ def gemm_plan(rows: int, n_out: int, k_dim: int, gated: bool):
     k_blocks = -(-k_dim // 64)
     stage_bytes = 16384 + bm * 128
     if rows <= 64:
-        if tiles * 6 <= 148 and k_blocks >= 24:
-            # few tiles (a narrow output): no more CTAs than SMs, each with the deepest ring
-            return bm, min(6, 148 // tiles), 8
+        def fits(splits, stages):       # every CTA resident at once
+            return tiles * splits <= 148 * ((227 * 1024) // (stages * stage_bytes + 2048))
+
+        # Measured inside the captured decode step (not kernel by kernel: what a product can have on
+        # its way before its predecessor ends depends on the room that predecessor leaves on an SM).
+        if tiles * 6 <= 148 and k_blocks >= 32:
+            # few tiles (a narrow output): eight CTAs a tile with six stages, two to an SM; where
+            # the stages are too large for that, six CTAs a tile with the deepest ring
+            return (bm, 8, 6) if fits(8, 6) else (bm, min(6, 148 // tiles), 8)
+        if tiles <= 74 and k_blocks >= 32:
+            # up to half as many tiles as SMs: six stages, two CTAs to an SM, about 1.3 CTAs per SM
+            splits = max(1, min(8, k_blocks // 4, 192 // tiles))
+            if fits(splits, 6):
+                return bm, splits, 6
         # otherwise: rings deeper than four stages lose (fewer CTAs fit on an SM); the product is
         # fastest with about 80% of the CTA slots taken and all CTAs resident at once; when three
         # stages let a third CTA onto each SM and that buys clearly more CTAs, three stages win
