@@ -560,24 +560,26 @@ def decode_attention_takes(head_dim: int, dtype) -> bool:
 
 
 def decode_splits(rows: int, kv_heads: int, groups: int, group_rows: int = 4, kv_hint: int = 0) -> int:
-    """How many parts to cut each row's keys into: as many as keep all blocks resident at once
-    (two per SM), so that no block waits for a second wave.
+    """How many parts to cut each row's keys into, so that every block is resident at once and the
+    SMs are busy.
 
     The tensor-core kernel (``group_rows`` 16) merges up to ``DECODE_CLUSTER_SPLITS`` parts inside a
-    thread-block cluster at no extra launch, so there every part may be as short as a page; beyond
-    that the merge is a kernel of its own, which pays only with twelve parts or more of three pages
-    at least (measured at 1 to 4 rows, 513 to 3,073 keys).  The CUDA-core kernel always merges with a
-    second kernel and wants three pages per part."""
+    thread-block cluster at no extra launch, and every part may be as short as a page.  Measured
+    inside the captured decode step at 3,073 keys: the step is fastest with at most 256 blocks (two
+    fit on an SM, 296 in all, but 280 or 288 blocks cost 12-17% of the whole step at 5, 6 and 12
+    rows), with 224 rather than 256 when that means 7 parts instead of 8, and never with more than 8
+    parts: 17 parts through scratch memory and the merge kernel lose 1-2% of the step to 8 in a
+    cluster at 1 and 2 rows.  The CUDA-core kernel always merges with a second kernel and wants three
+    pages per part."""
     blocks = rows * kv_heads * (-(-groups // group_rows))
-    want = max(1, min(32, (2 * 148) // blocks))
     pages = -(-kv_hint // PAGE_TOKENS) if kv_hint > 0 else None
     if group_rows < 16:
+        want = max(1, min(32, (2 * 148) // blocks))
         return want if pages is None else max(1, min(want, -(-pages // 3)))
-    in_cluster = want if pages is None else max(1, min(want, pages))
-    if in_cluster <= DECODE_CLUSTER_SPLITS:
-        return in_cluster
-    beyond = want if pages is None else min(want, -(-pages // 3))
-    return beyond if beyond >= 12 else DECODE_CLUSTER_SPLITS
+    want = max(1, min(DECODE_CLUSTER_SPLITS, 256 // blocks))
+    if want > 4 and want * blocks > 240:
+        want -= 1
+    return want if pages is None else max(1, min(want, pages))
 
 
 def decode_from_qkv_takes(head_dim: int, dtype) -> bool:

@@ -61,19 +61,21 @@ def test_product_plan_keeps_every_cta_resident_and_the_tile_in_the_ring():
 def test_decode_attention_splits_fit_one_wave_and_respect_the_length():
     from starter_b200.ops import decode_splits
 
-    assert decode_splits(1, 8, 4, 16) == 32
-    assert decode_splits(1, 8, 4, 16, kv_hint=3073) == 17        # many parts: scratch and a merge kernel
-    assert decode_splits(2, 8, 4, 16, kv_hint=3073) == 17
-    assert decode_splits(4, 8, 4, 16, kv_hint=3073) == 8         # nine would leave the cluster for little
-    assert decode_splits(1, 8, 4, 16, kv_hint=1025) == 8
-    assert decode_splits(1, 8, 4, 16, kv_hint=513) == 8
+    assert decode_splits(1, 8, 4, 16) == 8                       # never more parts than a cluster merges
+    assert decode_splits(1, 8, 4, 16, kv_hint=3073) == 8
+    assert decode_splits(2, 8, 4, 16, kv_hint=3073) == 8
+    assert decode_splits(4, 8, 4, 16, kv_hint=3073) == 7         # 224 blocks rather than 256
+    assert decode_splits(5, 8, 4, 16, kv_hint=3073) == 6         # 240 blocks, not 280
+    assert decode_splits(6, 8, 4, 16, kv_hint=3073) == 5
     assert decode_splits(8, 8, 4, 16, kv_hint=3073) == 4
+    assert decode_splits(12, 8, 4, 16, kv_hint=3073) == 2        # 192 blocks, not 288
+    assert decode_splits(1, 8, 4, 16, kv_hint=513) == 8
     assert decode_splits(8, 8, 4, 16, kv_hint=130) == 3          # a part is a page at least
     assert decode_splits(64, 8, 4, 16) == 1
     assert decode_splits(1, 8, 4, 16, kv_hint=10) == 1
     assert decode_splits(1, 8, 4, 4, kv_hint=513) == 3           # CUDA-core kernel: three pages a part
-    for rows in (1, 2, 5, 8, 30, 64):
-        assert rows * 8 * decode_splits(rows, 8, 4, 16) <= max(296, rows * 8)
+    for rows in (1, 2, 3, 5, 7, 8, 9, 10, 30, 64):
+        assert rows * 8 * decode_splits(rows, 8, 4, 16) <= max(256, rows * 8)
 
 
 def test_decode_graph_length_classes_never_exceed_the_length():
