@@ -10,9 +10,10 @@
 // of w, and each CTA's tensor memory receives the 128 rows of the accumulator that belong to it.
 // tcgen05.commit with cluster multicast hands the stage back to both CTAs' producers.
 //
-// The kernel is persistent: one CTA pair per pair of SMs, tiles dealt round robin with the row tiles
-// of one weight tile next to each other (so the weight tile is read from memory once and from L2 by
-// the others).  The accumulator is double buffered in tensor memory (2 x 256 columns): while the four
+// The kernel is persistent: one CTA pair per pair of SMs, tiles dealt round robin in an order that
+// keeps the tiles in flight close together (groups of row tiles, inside a group the row tiles of one
+// weight tile next to each other), so that operands are read from memory once per group and from L2
+// by the other tiles.  The accumulator is double buffered in tensor memory (2 x 256 columns): while the four
 // epilogue warps of each CTA read tile i back (tcgen05.ld), round it and write it out, the tensor
 // cores already work on tile i + 1.
 //
@@ -110,11 +111,25 @@ struct PromptGemmArgs {
   int bn;               // weight rows per tile (the MMA's N); with gated, bn / 2 gate and bn / 2 up rows
   int stages, gated;
   int m_tiles, n_tiles;
+  int group_m;          // row tiles per group (see pg_tile)
   unsigned long long wait_limit_ns;
   int withhold_kblock;  // >= 0: the first CTA leaves out its weight copy of this k-block of its first tile
 };
 
 // ------------------------------------------------------------------------------------------ kernel
+
+// Which tile is the t-th.  Tiles that run at the same time (one per CTA pair, consecutive t) should
+// share operands in L2: the row tiles are taken in groups of `group_m`; inside a group the tiles of
+// one weight tile follow each other, then the next weight tile.  So at any time the pairs work on
+// about group_m row tiles x a few weight tiles, the group's rows of x stay in L2 while all weight
+// tiles pass, and the weights are read from memory once per group.
+__device__ __forceinline__ void pg_tile(const PromptGemmArgs& args, int t, int& mt, int& nt) {
+  const int per_group = args.group_m * args.n_tiles;
+  const int g = t / per_group, r = t - g * per_group;
+  const int here = min(args.group_m, args.m_tiles - g * args.group_m);
+  nt = r / here;
+  mt = g * args.group_m + (r - nt * here);
+}
 
 // 32 values of row `grow` starting at column `col` of out, rounded to bfloat16; with a residual
 // stream, the rounded product is added to the stream's values first (the sum in float, rounded once
@@ -202,7 +217,8 @@ gemm_prompt_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     uint32_t parity = 1;          // flips at every wrap of the ring; the first pass waits for nothing
     bool gave_up = false;
     for (int t = pair; t < n_tiles_total && !gave_up; t += n_pairs) {
-      const int mt = t % args.m_tiles, nt = t / args.m_tiles;
+      int mt, nt;
+      pg_tile(args, t, mt, nt);
       const int m0 = mt * PG_TILE_M + (int)rank * PG_ROWS_PER_CTA;
       const int w0 = GATED ? (rank == 0 ? nt * half_n : args.n_out + nt * half_n) : nt * args.bn + (int)rank * half_n;
       const bool withheld_tile = rank == 0 && t == pair;
@@ -277,7 +293,8 @@ gemm_prompt_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
       // the whole warp goes on or the whole warp stops: the reads below are warp-wide instructions
       if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[b], (i >> 1) & 1, abort, limit))) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int mt = t % args.m_tiles, nt = t / args.m_tiles;
+      int mt, nt;
+      pg_tile(args, t, mt, nt);
       const int grow = mt * PG_TILE_M + (int)rank * PG_ROWS_PER_CTA + row;
       const int col0 = nt * out_per_tile;
       const uint32_t acc = lane_base + (uint32_t)b * PG_ACC_STRIDE;
@@ -434,6 +451,12 @@ static int pg_entry(const void* x, const void* w, void* out, const void* residua
   args.rows = rows; args.n_out = n_out; args.k_dim = k_dim;
   args.bn = bn; args.stages = stages; args.gated = gated;
   args.m_tiles = m_tiles; args.n_tiles = n_tiles;
+  // a group's rows of x (group_m x 256 x k x 2 bytes) should stay in L2 beside the weights passing by
+  long long group_m = (48ll << 20) / (512ll * k_dim);
+  if (group_m > 16) group_m = 16;
+  if (group_m < 1) group_m = 1;
+  if (group_m > m_tiles) group_m = m_tiles;
+  args.group_m = (int)group_m;
   args.wait_limit_ns = wait_limit_ns; args.withhold_kblock = withhold_kblock;
   const int smem = stages * stage_bytes + 1024;
   return gated ? pg_launch<true>(map_x, map_w, args, pairs, smem, s)

@@ -426,12 +426,13 @@ def test_a_wait_in_the_tensor_core_product_that_runs_out_is_reported(rows, n, k,
     (256, 256, 128, False, 256, 1), (512, 512, 192, False, 0, 0), (300, 200, 72, False, 0, 0),
     (300, 320, 136, False, 160, 0), (1, 64, 8, False, 64, 0), (700, 777, 264, False, 192, 3),
     (256, 128, 128, True, 256, 1), (700, 448, 264, True, 0, 0), (333, 192, 200, True, 128, 0),
-    (65, 100, 40, True, 64, 0), (2048, 2560, 1024, False, 0, 0), (1100, 1216, 2560, True, 0, 0)])
+    (65, 100, 40, True, 64, 0), (2048, 2560, 1024, False, 0, 0), (1100, 1216, 2560, True, 0, 0),
+    (4500, 300, 136, False, 0, 0), (4400, 128, 72, True, 0, 5)])
 def test_prompt_product(rows, n, k, gated, bn, pairs):
     """The CTA-pair product for many rows at sizes that are no multiples of its tiles (rows past the
     end of a 256-row tile, widths past the end of a weight tile, a k that ends inside a 64-wide
     block), every tile width, one pair or all of them (so that a pair works through several tiles
-    and both accumulators), plain and gated; twice, and bit-equal both times."""
+    and both accumulators), more row tiles than one group holds, plain and gated; twice, and bit-equal both times."""
     from starter_b200 import ops
 
     x = rand(rows, k, dtype="bfloat16", seed=52)
