@@ -567,10 +567,10 @@ def decode_splits(rows: int, kv_heads: int, groups: int, group_rows: int = 4, kv
     thread-block cluster at no extra launch, and every part may be as short as a page.  Measured
     inside the captured decode step at 3,073 keys: the step is fastest with at most 256 blocks (two
     fit on an SM, 296 in all, but 280 or 288 blocks cost 12-17% of the whole step at 5, 6 and 12
-    rows), with 224 rather than 256 when that means 7 parts instead of 8, and never with more than 8
-    parts: 17 parts through scratch memory and the merge kernel lose 1-2% of the step to 8 in a
-    cluster at 1 and 2 rows.  The CUDA-core kernel always merges with a second kernel and wants three
-    pages per part."""
+    rows), with 224 rather than 256 when that means 7 parts instead of 8, and with no more than 8
+    parts at 3,073 keys: 17 parts through scratch memory and the merge kernel lose 1-2% of the step
+    to 8 in a cluster at 1 and 2 rows.  The CUDA-core kernel always merges with a second kernel and
+    wants three pages per part."""
     blocks = rows * kv_heads * (-(-groups // group_rows))
     pages = -(-kv_hint // PAGE_TOKENS) if kv_hint > 0 else None
     if group_rows < 16:
@@ -579,7 +579,23 @@ def decode_splits(rows: int, kv_heads: int, groups: int, group_rows: int = 4, kv
     want = max(1, min(DECODE_CLUSTER_SPLITS, 256 // blocks))
     if want > 4 and want * blocks > 240:
         want -= 1
-    return want if pages is None else max(1, min(want, pages))
+    if pages is None:
+        return want
+    want = max(1, min(want, pages))
+    # Few rows of many keys: 8 parts a row leave most SMs without a block, and a block streams about
+    # 60 GB/s.  More parts through scratch memory cost a merge kernel (3 us) and fill the SMs.
+    # Estimated both ways in microseconds from the bytes (a page of keys and values of a 128-wide
+    # head is 32 KB) and taken when the estimate says so; the crossover it gives for one row of 8
+    # key/value heads, 6,700 keys, lies between the measured 3,073 (cluster faster by 0.7 us a
+    # layer) and 16,384 (scratch faster by 6.2 us).
+    more = max(1, min(32, 256 // blocks, pages // 3))
+    if more >= 12 and more > want:
+        megabytes = blocks * pages * 0.032768
+        in_cluster = megabytes / min(6.5, want * blocks * 0.06)
+        through_scratch = 3.0 + megabytes / min(6.5, more * blocks * 0.06)
+        if through_scratch < in_cluster:
+            return more
+    return want
 
 
 def decode_from_qkv_takes(head_dim: int, dtype) -> bool:

@@ -70,12 +70,16 @@ def test_decode_attention_splits_fit_one_wave_and_respect_the_length():
     assert decode_splits(8, 8, 4, 16, kv_hint=3073) == 4
     assert decode_splits(12, 8, 4, 16, kv_hint=3073) == 2        # 192 blocks, not 288
     assert decode_splits(1, 8, 4, 16, kv_hint=513) == 8
+    assert decode_splits(1, 8, 4, 16, kv_hint=16384) == 32       # one long row: many parts through scratch
+    assert decode_splits(1, 8, 4, 16, kv_hint=6000) == 8
+    assert decode_splits(2, 8, 4, 16, kv_hint=16384) == 8        # two rows fill the SMs from a cluster
     assert decode_splits(8, 8, 4, 16, kv_hint=130) == 3          # a part is a page at least
     assert decode_splits(64, 8, 4, 16) == 1
     assert decode_splits(1, 8, 4, 16, kv_hint=10) == 1
     assert decode_splits(1, 8, 4, 4, kv_hint=513) == 3           # CUDA-core kernel: three pages a part
     for rows in (1, 2, 3, 5, 7, 8, 9, 10, 30, 64):
-        assert rows * 8 * decode_splits(rows, 8, 4, 16) <= max(256, rows * 8)
+        for keys in (0, 700, 3073, 20000):
+            assert rows * 8 * decode_splits(rows, 8, 4, 16, kv_hint=keys) <= max(256, rows * 8)
 
 
 def test_decode_graph_length_classes_never_exceed_the_length():
