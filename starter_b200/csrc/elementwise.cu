@@ -23,6 +23,24 @@ __global__ void embedding_kernel(const int* __restrict__ tokens, const T* __rest
   }
   const T* src = table + (size_t)tok * hidden;
   T* dst = out + (size_t)row * hidden;
+  constexpr int N = 16 / sizeof(T);
+  if (!bad && hidden % N == 0 && (((uintptr_t)table | (uintptr_t)out) & 15) == 0) {
+    // 16 bytes a thread and all of a thread's loads in flight together: the row comes from memory
+    // nobody has touched for a step, and this kernel stands alone between two steps
+    const uint4* src4 = reinterpret_cast<const uint4*>(src);
+    uint4* dst4 = reinterpret_cast<uint4*>(dst);
+    const int n = hidden / N;
+    uint4 v[4];
+    for (int c0 = threadIdx.x; c0 < n; c0 += 4 * blockDim.x) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (c0 + i * blockDim.x < n) v[i] = src4[c0 + i * blockDim.x];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (c0 + i * blockDim.x < n) dst4[c0 + i * blockDim.x] = v[i];
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = bad ? from_f<T>(0.f) : src[c];
 }
 
