@@ -290,3 +290,31 @@ def test_prompts_long_enough_for_the_prompt_product(tmp_path_factory, name, dtyp
     assert_close(torch.cat(rows), want_a, dtype, f"{name} 600 + 90 + 10 x 1")
     runner.check_status()
     runner.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_one_long_sequence_decodes_through_many_parts(tmp_path_factory, dtype):
+    """One sequence of 6,000 tokens: alone it cannot fill the GPU from a cluster's 8 parts, so its
+    one-token steps cut the keys into many parts that meet in scratch memory and a merge kernel
+    (the choice is asserted, so that the test keeps covering that path); the prompt before them walks
+    94 pages through the prompt attention and several groups of row tiles through the prompt product."""
+    from starter_b200 import ops
+    from starter_b200.engine import StepEntry
+
+    name = "A"
+    _, cfg, w = model_case(tmp_path_factory, name)
+    groups = cfg["num_attention_heads"] // cfg["num_key_value_heads"]
+    assert ops.decode_splits(1, cfg["num_key_value_heads"], groups, 16, kv_hint=5995) > ops.DECODE_CLUSTER_SPLITS
+    runner = runner_for(tmp_path_factory, name, dtype, max_tokens=64 * 95)
+    seq = random_prompt(6000, cfg["vocab_size"], 81)
+    want = plain.plain_forward(cfg, w, seq)
+    head = 5990
+    slot = runner.open_sequence()
+    rows = [runner.step([StepEntry(slot, seq[:head], [0, 1000, head - 1])])]
+    rows += [runner.step([StepEntry(slot, [t], [0])]) for t in seq[head:]]
+    runner.close_sequence(slot)
+    got = torch.cat(rows)
+    places = [0, 1000, head - 1] + list(range(head, len(seq)))
+    assert_close(got, want[places], dtype, f"{name} 5,990 tokens and 10 x 1")
+    runner.check_status()
+    runner.cache.check()
