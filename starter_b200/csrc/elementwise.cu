@@ -202,6 +202,62 @@ __global__ void rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ delt
   }
 }
 
+// Many rows: a warp per row.  With a block per row a 2,048-row prompt is 2,048 short-lived blocks
+// whose chain (load, block reduction with two barriers, store) is latency, in two waves: 10 us for
+// 21 MB.  A warp per row needs no barrier, 64 rows are in flight on an SM and all rows at once.  The
+// row is read twice (the second time from L1/L2, where this lane's own writes of the sum are).
+template <typename T, typename W, bool ADD>
+__global__ void rmsnorm_warp_kernel(T* __restrict__ x, const T* __restrict__ delta,
+                                    const W* __restrict__ gain, T* __restrict__ y, int n_rows,
+                                    int hidden, float eps) {
+  constexpr int N = Vec16<T>::N;
+  pdl_trigger();
+  pdl_wait();
+  SB_BEHIND_WAIT(delta);
+  const int row = (int)((blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
+  if (row >= n_rows) return;
+  T* xr = x + (size_t)row * hidden;
+  const T* dr = ADD ? delta + (size_t)row * hidden : nullptr;
+  T* yr = y + (size_t)row * hidden;
+  const int vecs = hidden / N;
+  float ss = 0.f;
+#pragma unroll 4
+  for (int i = lane; i < vecs; i += 32) {
+    float v[N];
+    load_vec16<T, N>(xr + i * N, v);
+    if (ADD) {
+      float d[N];
+      load_vec16<T, N>(dr + i * N, d);
+#pragma unroll
+      for (int j = 0; j < N; j += 2) {
+        v[j] += d[j];
+        v[j + 1] += d[j + 1];
+        rnd2<T>(v[j], v[j + 1]);
+      }
+      store_exact16<T, N>(xr + i * N, v);
+    }
+#pragma unroll
+    for (int j = 0; j < N; ++j) ss += v[j] * v[j];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float inv = rsqrtf(ss / (float)hidden + eps);
+#pragma unroll 4
+  for (int i = lane; i < vecs; i += 32) {
+    float v[N], g[N], o[N];
+    load_vec16<T, N>(xr + i * N, v);
+    load_gain<W, N>(gain + i * N, g);
+#pragma unroll
+    for (int j = 0; j < N; j += 2) {
+      float a = v[j] * inv, b = v[j + 1] * inv;
+      rnd2<T>(a, b);
+      o[j] = a * g[j];
+      o[j + 1] = b * g[j + 1];
+    }
+    store_vec16<T, N>(yr + i * N, o);
+  }
+}
+
 template <typename T, typename W>
 static int launch_rmsnorm(void* x, const void* delta, const void* gain, void* y, const int* rows,
                           int n_rows, int hidden, float eps, cudaStream_t s) {
@@ -213,6 +269,13 @@ static int launch_rmsnorm(void* x, const void* delta, const void* gain, void* y,
   T* yp = (T*)y;
   constexpr int N = 16 / sizeof(T);
   const bool aligned = hidden % N == 0 && (((uintptr_t)x | (uintptr_t)delta | (uintptr_t)y) & 15) == 0;
+  if (aligned && !rows && n_rows > 256 && x != y) {
+    const int threads_w = 256;                       // 8 rows a block
+    const int blocks = (n_rows + 7) / 8;
+    if (delta)
+      return launch_dependent(rmsnorm_warp_kernel<T, W, true>, dim3(blocks), dim3(threads_w), 0, s, xp, dp, gp, yp, n_rows, hidden, eps);
+    return launch_dependent(rmsnorm_warp_kernel<T, W, false>, dim3(blocks), dim3(threads_w), 0, s, xp, dp, gp, yp, n_rows, hidden, eps);
+  }
   if (aligned && hidden <= 4 * N * 1024) {
     int vt = 32;
     while (vt * N * 2 < hidden && vt < 1024) vt *= 2;   // about two vectors per thread

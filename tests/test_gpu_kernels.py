@@ -61,6 +61,31 @@ def test_rmsnorm_alone_with_the_residual_sum_and_on_chosen_rows(dtype, hidden):
 
 
 @pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("hidden", [24, 1000, 2560, 5128])
+def test_rmsnorm_of_many_rows(dtype, hidden):
+    """More than 256 rows take the warp-per-row kernel: alone and with the residual sum, a row count
+    that does not fill the last block, and the same values as the few-row kernel gives row by row."""
+    from starter_b200 import ops
+
+    n = 301
+    x, d = rand(n, hidden, dtype=dtype, seed=4), rand(n, hidden, dtype=dtype, seed=5)
+    gain = (1 + 0.1 * rand(hidden, seed=6)).to(DT[dtype])
+    eps = 1e-6
+    got = ops.rmsnorm(dev(x), dev(gain), eps)
+    assert torch.allclose(got.cpu().float(), plain.plain_rms_norm(x, gain, eps).float(), **TOL[dtype])
+    few = torch.cat([ops.rmsnorm(dev(x[i:i + 100].contiguous()), dev(gain), eps) for i in range(0, n, 100)])
+    assert torch.allclose(got.float(), few.float(), **TOL[dtype])
+    total = x + d
+    res = dev(x.clone())
+    got = ops.rmsnorm(res, dev(gain), eps, delta=dev(d))
+    assert torch.equal(res.cpu(), total)
+    assert torch.allclose(got.cpu().float(), plain.plain_rms_norm(total, gain, eps).float(), **TOL[dtype])
+    if dtype == "bfloat16":
+        got = ops.rmsnorm(dev(x), dev(gain.float()), eps)
+        assert torch.allclose(got.cpu().float(), plain.plain_rms_norm(x, gain, eps).float(), **TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", list(DT))
 def test_swiglu(dtype):
     from starter_b200 import ops
 
