@@ -45,12 +45,13 @@ DECODE_AT = 3072  # 2,048 prompt tokens + 1,024 decoded: the middle of the gener
 
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    out = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    out = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
     if os.path.isfile(path):
         try:
             raw = json.load(open(path))
             out["hbm_gbs"] = float(raw.get("hbm_gbs", out["hbm_gbs"]))
             out["bf16_tflops"] = float(raw.get("bf16_tflops", out["bf16_tflops"]))
+            out["bf16_tflops_sustained"] = float(raw.get("bf16_tflops_sustained", out["bf16_tflops_sustained"]))
             out["source"] = "measured"
         except Exception:  # noqa: BLE001
             pass
@@ -357,7 +358,10 @@ def main() -> int:
     attn = 4 * nh * d * PROMPT * (PROMPT + 1) / 2
     prefill_flops = layers * (per_token * PROMPT + attn) + 2 * h * vocab
     prefill = {"value": round(PROMPT / prefill_ms * 1e3, 1), "tokens": PROMPT, "ms": round(prefill_ms, 3),
-               "frac": round(prefill_flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+               "frac": round(prefill_flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+               # the same against the vendor GEMM's throughput in a seconds-long loop under the power
+               # cap: the prompt step is timed over several back-to-back repetitions
+               "frac_of_sustained": round(prefill_flops / (prefill_ms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)}
 
     # ---------------------------------------------------------------- decode, device-timed
     def decode_point(batch):
