@@ -29,6 +29,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "tensor_map.cuh"
 
 #define TC_BQ 128
 #define TC_BK 128
@@ -554,37 +555,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
 // ------------------------------------------------------------------------------------------ host
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)p;
-  }
-  return fn;
-}
-
-// A [rows, cols] row-major bfloat16 matrix read in boxes of [box_rows x 64] with 128-byte swizzle.
-static int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return -3;
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
-  cuuint32_t elem[2] = {1, 1};
-  CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims, strides, box, elem,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return rc == CUDA_SUCCESS ? 0 : -4;
-}
-
 template <int D>
 static int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out,
                   const int* block_table, int table_stride, const int* seq_slot, const int* seq_q_start,
@@ -633,12 +603,12 @@ int sb_attention_prefill_tc(const void* q, void* out, const void* k_store, const
   if (head_dim != 64 && head_dim != 128) return -2;
   if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)k_store | (uintptr_t)v_store) & 15) return -2;
   CUtensorMap mq, mk, mv;
-  int rc = make_map(&mq, q, n_tokens, (long long)heads * head_dim, TC_BQ);
+  int rc = sb_make_map(&mq, q, n_tokens, (long long)heads * head_dim, TC_BQ);
   if (rc) return rc;
   const long long kv_rows = (long long)n_pages * kv_heads * SB_PAGE_TOKENS;
-  rc = make_map(&mk, k_store, kv_rows, head_dim, SB_PAGE_TOKENS);
+  rc = sb_make_map(&mk, k_store, kv_rows, head_dim, SB_PAGE_TOKENS);
   if (rc) return rc;
-  rc = make_map(&mv, v_store, kv_rows, head_dim, SB_PAGE_TOKENS);
+  rc = sb_make_map(&mv, v_store, kv_rows, head_dim, SB_PAGE_TOKENS);
   if (rc) return rc;
 #define ARGS mq, mk, mv, out, block_table, table_stride, seq_slot, seq_q_start, seq_q_len, seq_kv_len, \
              tile_seq, tile_first, n_tiles, heads, kv_heads, scale, window, status, list_of_blocks, s

@@ -31,6 +31,7 @@
 // the grid counter) gives up after a time limit, raises bit 32 of *status and a flag in the sync
 // area that makes all other CTAs (and later launches, until the host clears it) give up at once.
 #include "tcgen05.cuh"
+#include "tensor_map.cuh"
 
 #define DC_TILE_N 128
 #define DC_TILE_K 64
@@ -568,37 +569,6 @@ dense_chain_kernel(const __grid_constant__ DcMaps maps, const __grid_constant__ 
 
 // ------------------------------------------------------------------------------------------ host
 
-typedef CUresult (*DcEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                               CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                               CUtensorMapFloatOOBfill);
-
-static DcEncodeFn dc_encode_fn() {
-  static DcEncodeFn fn = nullptr;
-  if (!fn) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (DcEncodeFn)ptr;
-  }
-  return fn;
-}
-
-// A [rows, k] row-major bfloat16 matrix read in boxes of [box_rows x 64] with 128-byte swizzle.
-static int dc_make_map(CUtensorMap* map, const void* base, long long rows, int k_dim, int box_rows) {
-  DcEncodeFn fn = dc_encode_fn();
-  if (!fn) return -3;
-  cuuint64_t dims[2] = {(cuuint64_t)k_dim, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)k_dim * 2};
-  cuuint32_t box[2] = {DC_TILE_K, (cuuint32_t)box_rows};
-  cuuint32_t elem[2] = {1, 1};
-  CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims, strides, box, elem,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return rc == CUDA_SUCCESS ? 0 : -4;
-}
-
 static int dc_sm_count() {
   static int count[64];
   int device = 0;
@@ -696,9 +666,9 @@ int sb_dense_chain(const long long* desc, const float* eps, int n_stages, int ro
             (int)desc[16 * (i + 1) + 1] != st.n_out || st.gated)
           return -2;
       }
-      int rc = dc_make_map(&maps.w[lin], w, st.gated ? 2ll * st.n_out : st.n_out, st.k_dim, 64);
+      int rc = sb_make_map(&maps.w[lin], w, st.gated ? 2ll * st.n_out : st.n_out, st.k_dim, 64);
       if (rc) return rc;
-      rc = dc_make_map(&maps.x[lin], x, rows, st.k_dim, bm);
+      rc = sb_make_map(&maps.x[lin], x, rows, st.k_dim, bm);
       if (rc) return rc;
       ++lin;
     } else if (st.kind == DC_KIND_NORM) {

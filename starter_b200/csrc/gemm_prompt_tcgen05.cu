@@ -26,6 +26,7 @@
 // drain, free their tensor memory and return; sb_gemm_prompt_withheld leaves out one weight copy on
 // purpose so that this path can be exercised without a fault.
 #include "tcgen05.cuh"
+#include "tensor_map.cuh"
 
 #define PG_ROWS_PER_CTA 128
 #define PG_TILE_M 256
@@ -331,55 +332,6 @@ gemm_prompt_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
 
 // ------------------------------------------------------------------------------------------ host
 
-typedef CUresult (*PgEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                    CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                    CUtensorMapFloatOOBfill);
-
-static PgEncodeTiledFn pg_encode_fn() {
-  static PgEncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (PgEncodeTiledFn)p;
-  }
-  return fn;
-}
-
-// A [rows, k] row-major bfloat16 matrix read in boxes of [box_rows x 64] with 128-byte swizzle.  The
-// last maps made are kept (the same weights and recycled activation buffers come back every step).
-struct PgMapKey {
-  const void* base;
-  long long rows;
-  int k_dim, box_rows;
-  bool operator==(const PgMapKey& o) const {
-    return base == o.base && rows == o.rows && k_dim == o.k_dim && box_rows == o.box_rows;
-  }
-};
-struct PgMapSlot { PgMapKey key; CUtensorMap map; bool used; };
-
-static int pg_make_map(CUtensorMap* map, const void* base, long long rows, int k_dim, int box_rows) {
-  static thread_local PgMapSlot cache[512];
-  const PgMapKey key = {base, rows, k_dim, box_rows};
-  const size_t h = (((uintptr_t)base >> 8) * 0x9E3779B97F4A7C15ull + (size_t)box_rows * 31 + (size_t)rows) >> 20;
-  PgMapSlot& slot = cache[h & 511];
-  if (slot.used && slot.key == key) { *map = slot.map; return 0; }
-  PgEncodeTiledFn fn = pg_encode_fn();
-  if (!fn) return -3;
-  cuuint64_t dims[2] = {(cuuint64_t)k_dim, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)k_dim * 2};
-  cuuint32_t box[2] = {PG_TILE_K, (cuuint32_t)box_rows};
-  cuuint32_t elem[2] = {1, 1};
-  CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims, strides, box, elem,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (rc != CUDA_SUCCESS) return -4;
-  slot.key = key; slot.map = *map; slot.used = true;
-  return 0;
-}
-
 static int pg_sm_count() {
   static int sms = 0;
   if (!sms) {
@@ -441,9 +393,9 @@ static int pg_entry(const void* x, const void* w, void* out, const void* residua
   const long long total = (long long)m_tiles * n_tiles;
   if (total < pairs) pairs = (int)total;
   CUtensorMap map_x, map_w;
-  int rc = pg_make_map(&map_x, x, rows, k_dim, PG_ROWS_PER_CTA);
+  int rc = sb_make_map(&map_x, x, rows, k_dim, PG_ROWS_PER_CTA);
   if (rc) return rc;
-  rc = pg_make_map(&map_w, w, gated ? 2ll * n_out : n_out, k_dim, bn / 2);
+  rc = sb_make_map(&map_w, w, gated ? 2ll * n_out : n_out, k_dim, bn / 2);
   if (rc) return rc;
   PromptGemmArgs args;
   if (residual && gated) return -2;

@@ -23,6 +23,7 @@
 // activation copy on purpose: the stage it belongs to never completes, the wait on it runs out and
 // the kernel must come back with the status bit set.
 #include "tcgen05.cuh"
+#include "tensor_map.cuh"
 
 #define TILE_N 128      // weight rows per CTA (MMA M)
 #define TILE_K 64       // k per stage: 128 bytes of bfloat16, one swizzle atom
@@ -304,57 +305,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
 // ------------------------------------------------------------------------------------------ host
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)p;
-  }
-  return fn;
-}
-
-// A [rows, k] row-major bfloat16 matrix read in boxes of [box_rows x 64] with 128-byte swizzle.
-// Encoding a map costs a microsecond or two on the host, and the same matrices (every weight, and
-// activation buffers the allocator hands out again) come back step after step: the last maps are
-// kept in a small direct-mapped table keyed by everything a map is made of.
-struct MapKey {
-  const void* base;
-  long long rows;
-  int k_dim, box_rows;
-  bool operator==(const MapKey& o) const {
-    return base == o.base && rows == o.rows && k_dim == o.k_dim && box_rows == o.box_rows;
-  }
-};
-struct MapSlot { MapKey key; CUtensorMap map; bool used; };
-
-static int make_map(CUtensorMap* map, const void* base, int rows, int k_dim, int box_rows) {
-  static thread_local MapSlot cache[512];
-  const MapKey key = {base, rows, k_dim, box_rows};
-  const size_t h = (((uintptr_t)base >> 8) * 0x9E3779B97F4A7C15ull + (size_t)box_rows * 31 + (size_t)rows) >> 20;
-  MapSlot& slot = cache[h & 511];
-  if (slot.used && slot.key == key) { *map = slot.map; return 0; }
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return -3;
-  cuuint64_t dims[2] = {(cuuint64_t)k_dim, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)k_dim * 2};
-  cuuint32_t box[2] = {TILE_K, (cuuint32_t)box_rows};
-  cuuint32_t elem[2] = {1, 1};
-  CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims, strides, box, elem,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (rc != CUDA_SUCCESS) return -4;
-  slot.key = key; slot.map = *map; slot.used = true;
-  return 0;
-}
-
 template <int BM, bool GATED>
 static int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const GemmArgs& args, int tiles,
                   int m_tiles, cudaStream_t s) {
@@ -391,9 +341,9 @@ static int gemm_entry(const void* x, const void* w, void* out, int rows, int n_o
   const int m_tiles = (rows + bm - 1) / bm;
   const int w_rows = gated ? 2 * n_out : n_out;
   CUtensorMap map_w, map_x;
-  int rc = make_map(&map_w, w, w_rows, k_dim, 64);
+  int rc = sb_make_map(&map_w, w, w_rows, k_dim, 64);
   if (rc) return rc;
-  rc = make_map(&map_x, x, rows, k_dim, bm);
+  rc = sb_make_map(&map_x, x, rows, k_dim, bm);
   if (rc) return rc;
   GemmArgs args;
   args.out = out; args.status = status;
