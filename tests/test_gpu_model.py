@@ -318,3 +318,34 @@ def test_one_long_sequence_decodes_through_many_parts(tmp_path_factory, dtype):
     assert_close(got, want[places], dtype, f"{name} 5,990 tokens and 10 x 1")
     runner.check_status()
     runner.cache.check()
+
+
+@pytest.mark.parametrize("name", ["B", "C"])
+def test_random_batches_of_short_and_long_prompts_generate_right_tokens(tmp_path_factory, name):
+    """Generation in bfloat16 over batches drawn at random: 1 to 8 sequences, prompts of 1 to 700
+    tokens in one batch (so prompt steps of every kernel class), 1 to 17 new tokens, batch after
+    batch on one engine.  Every token drawn must be, by the plain float32 model on the engine's own
+    prefix, within the logit tolerance of the best token."""
+    import random
+
+    from gpu_helpers import BF16_TOL
+    from starter_b200 import Engine
+
+    folder, cfg, w = model_case(tmp_path_factory, name)
+    engine = Engine(folder, dtype="bfloat16", max_batch=8)
+    rng = random.Random(11)
+    for _ in range(5):
+        n = rng.choice([1, 2, 3, 5, 8])
+        prompts = [random_prompt(rng.choice([1, 2, 63, 65, 130, 300, 520, 700]), cfg["vocab_size"], rng.randrange(10 ** 6))
+                   for _ in range(n)]
+        new = rng.choice([1, 2, 5, 17])
+        for prompt, done in zip(prompts, engine.complete(prompts, new)):
+            seq = list(prompt)
+            for tok in done.tokens:
+                logits = plain.plain_forward(cfg, w, seq)[-1]
+                margin = 2 * BF16_TOL * float(logits.abs().max())
+                assert logits[tok].item() >= logits.max().item() - margin, (len(prompt), len(seq))
+                seq.append(tok)
+        assert engine.runner.cache.slots.held_count == 0
+        engine.runner.cache.check()
+        engine.runner.check_status()
