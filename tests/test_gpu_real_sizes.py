@@ -103,28 +103,29 @@ def test_real_layer_sizes_graph_decode_of_a_full_batch(tmp_path_factory):
         runner.close_sequence(s)
 
 
-def test_real_layer_sizes_sixty_four_unequal_sequences(tmp_path_factory):
-    """A batch of 64 (the widest tiles of every product, one part per sequence in the attention):
-    the prompts in one step, then one eager and one captured single-token step, every row against
-    the plain implementation."""
+@pytest.mark.parametrize("n,grow", [(64, 5), (100, 3)])
+def test_real_layer_sizes_many_unequal_sequences(tmp_path_factory, n, grow):
+    """A batch of 64 (the widest of the usual tiles of every product, one part per sequence in the
+    attention) and one of 100 (128-row tiles in the few-row product): the prompts in one step, then
+    one eager and one captured single-token step, every row against the plain implementation."""
     from starter_b200.engine import ModelRunner, StepEntry, load_model
 
     folder, cfg, w = real_case(tmp_path_factory)
     vocab = cfg["vocab_size"]
-    seqs = [random_prompt(3 + 5 * i + 2, vocab, 1200 + i) for i in range(64)]     # prompt + 2 tokens
+    seqs = [random_prompt(3 + grow * i + 2, vocab, 1200 + i) for i in range(n)]     # prompt + 2 tokens
     want = [plain.plain_forward(cfg, w, s) for s in seqs]
-    runner = ModelRunner(load_model(folder, "bfloat16"), max_tokens=64 * 6 * 64, max_sequences=64)
+    runner = ModelRunner(load_model(folder, "bfloat16"), max_tokens=n * 6 * 64, max_sequences=n)
     slots = [runner.open_sequence() for _ in seqs]
     heads = [len(s) - 2 for s in seqs]
     out = runner.step([StepEntry(s, q[:h], [h - 1]) for s, q, h in zip(slots, seqs, heads)])
-    assert_close(out, torch.stack([want[i][heads[i] - 1] for i in range(64)]), "bfloat16", "64 prompts, last places")
+    assert_close(out, torch.stack([want[i][heads[i] - 1] for i in range(n)]), "bfloat16", f"{n} prompts, last places")
     out = runner.step([StepEntry(s, [q[h]], [0]) for s, q, h in zip(slots, seqs, heads)])
-    assert_close(out, torch.stack([want[i][heads[i]] for i in range(64)]), "bfloat16", "64 rows, eager step")
+    assert_close(out, torch.stack([want[i][heads[i]] for i in range(n)]), "bfloat16", f"{n} rows, eager step")
     runner.decode_tokens([StepEntry(s, [q[h + 1]], [0]) for s, q, h in zip(slots, seqs, heads)],
-                         [0.0] * 64, [0] * 64)
+                         [0.0] * n, [0] * n)
     got = runner.graphs.logits[runner.graphs.last_key]
-    assert got.shape[0] == 64
-    assert_close(got, torch.stack([want[i][heads[i] + 1] for i in range(64)]), "bfloat16", "64 rows, captured step")
+    assert got.shape[0] == n
+    assert_close(got, torch.stack([want[i][heads[i] + 1] for i in range(n)]), "bfloat16", f"{n} rows, captured step")
     for s in slots:
         runner.close_sequence(s)
     runner.check_status()
