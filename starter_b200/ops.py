@@ -10,6 +10,7 @@ refused with an error that names it.
 from __future__ import annotations
 
 import ctypes
+import functools
 
 import torch
 
@@ -255,6 +256,7 @@ def tensor_core_ok(x, weight, gated, n_out) -> bool:
     return True
 
 
+@functools.lru_cache(maxsize=4096)     # asked once per launch, with the same few shapes step after step
 def gemm_plan(rows: int, n_out: int, k_dim: int, gated: bool):
     """``(bm, splits, stages)``: activation rows per tile; how many CTAs (one cluster) share a tile's
     k range; how deep the ring of shared-memory stages is.
@@ -559,6 +561,7 @@ def decode_attention_takes(head_dim: int, dtype) -> bool:
     return head_dim in DECODE_HEAD_DIMS and head_dim * dtype.itemsize <= 512
 
 
+@functools.lru_cache(maxsize=4096)
 def decode_splits(rows: int, kv_heads: int, groups: int, group_rows: int = 4, kv_hint: int = 0) -> int:
     """How many parts to cut each row's keys into, so that every block is resident at once and the
     SMs are busy.
